@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse gated-FFN hot path at the 1.5B decode shape.
+
+Workload (``config.workload``): the FFN stack of a random-init 1.5B-shape sparse
+decoder - 28 layers, d_model 2048, d_ff 8192, bf16 weights ~N(0, 0.02), gate
+density about 2 % with log-normal(sigma=1) per-neuron firing rates - at a decode
+batch of B tokens (default 32).  One step = one pass of all 28 sparse FFN layers
+over one batch of synthetic activations; ``value`` = B / step time (tokens/s).
+The 2.8 GB of weights exceed the 126 MB L2, so every step streams them from HBM
+(no L2 flush needed).
+
+Legs printed in ONE JSON line by rank 0:
+  value        device-resident inputs, the step replayed as a CUDA graph
+  e2e          the same stack through the public ``TwELLGatedMLP`` modules with
+               pinned-host inputs and outputs (H2D + D2H inside the timed region)
+  roofline     the dominant kernel (gate GEMV + TwELL pack) timed alone
+  cpu_baseline the dense torch formula on the host cores (bounded sample)
+
+``--impl reference`` times the reference's torch CPU formulation
+(SparseMLP._forward_mlp_inference_logic) on the host cores instead.
+With ``--gpus N`` (torchrun) d_ff is sharded over the ranks and the partial FFN
+outputs are summed with one NCCL all-reduce per layer (strong scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+LAYERS, D_MODEL, D_FF = 28, 2048, 8192
+DENSITY, SKEW = 0.02, 1.0
+METRIC = "sparse_ffn_decode_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--d-model", type=int, default=D_MODEL)
+    ap.add_argument("--d-ff", type=int, default=D_FF)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return float(j["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------
+# clocks sampling
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------
+# workload
+# ----------------------------------------------------------------------------
+def shard_range(h: int, rank: int, world: int):
+    """Tile-granular (256-neuron) contiguous split of d_ff; uneven shards allowed."""
+    tiles = h // 256
+    base, rem = divmod(tiles, world)
+    start = rank * base + min(rank, rem)
+    n = base + (1 if rank < rem else 0)
+    return start * 256, (start + n) * 256
+
+
+def build_layers(args, device, rank, world):
+    from sparser_faster_llms_b200 import synthetic
+    d, h = args.d_model, args.d_ff
+    h0, h1 = shard_range(h, rank, world)
+    layers = []
+    for l in range(args.layers):
+        gen = torch.Generator(device=device).manual_seed(1000 + l)
+        w = torch.randn(3, h, d, generator=gen, device=device, dtype=torch.float32) * 0.02
+        cg = torch.Generator().manual_seed(2000 + l)
+        rates = synthetic.neuron_rates(h, DENSITY, SKEW, cg)
+        shift = (0.02 * (d - 1) ** 0.5 * torch.special.ndtri(rates)).float().to(device)
+        w[0, :, 0] = shift  # bias folded into feature 0 (tokens carry x[:, 0] = 1)
+        wb = w[:, h0:h1].to(torch.bfloat16).contiguous()
+        layers.append((wb[0], wb[1], wb[2]))
+        del w
+    gen = torch.Generator(device=device).manual_seed(7)
+    x = torch.randn(args.layers, args.batch, d, generator=gen, device=device)
+    x[:, :, 0] = 1.0
+    return layers, x.to(torch.bfloat16).contiguous(), (h0, h1)
+
+
+def capture(fn, device):
+    """Warm up ``fn`` on a side stream, then capture it into a CUDA graph."""
+    s = torch.cuda.Stream(device)
+    s.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            fn()
+    torch.cuda.current_stream(device).wait_stream(s)
+    torch.cuda.synchronize(device)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
+def time_replays(run, steps, warmup, device, dist_on):
+    import torch.distributed as dist
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize(device)
+    if dist_on:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize(device)
+    if dist_on:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if dist_on:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from sparser_faster_llms_b200 import _lib, twell
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist_on = world > 1
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if dist_on:
+        dist.init_process_group("nccl", device_id=device)
+    _lib.load_library()
+
+    layers, x, (h0, h1) = build_layers(args, device, rank, world)
+    hl = h1 - h0
+    L, B, d = args.layers, args.batch, args.d_model
+    packed = torch.zeros(B, twell.packed_width(hl), device=device, dtype=torch.uint32)
+    out = torch.empty(L, B, d, device=device, dtype=torch.bfloat16)
+
+    def step():
+        for l, (g, u, dn) in enumerate(layers):
+            _lib.call("b200_twell_gated_mlp", device, x[l].data_ptr(), g.data_ptr(), None,
+                      u.data_ptr(), dn.data_ptr(), packed.data_ptr(), out[l].data_ptr(),
+                      B, d, hl, 8, 0)
+            if dist_on:
+                dist.all_reduce(out[l])
+
+    def pack_only():
+        for l, (g, u, dn) in enumerate(layers):
+            _lib.call("b200_twell_pack", device, x[l].data_ptr(), g.data_ptr(), None,
+                      packed.data_ptr(), B, d, hl, 8)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    graph = capture(step, device)
+    ms_step = time_replays(graph.replay, args.steps, args.warmup, device, dist_on)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # dominant kernel alone (per-launch time, CUDA events on the launching stream)
+    g_pack = capture(pack_only, device)
+    ms_pack = time_replays(g_pack.replay, max(10, args.steps // 2), 3, device, False) / L
+    # statistics of the last slab for the byte model
+    torch.cuda.synchronize(device)
+    counts = packed.view(torch.int32)[:, ::32].long()
+    nnz_per_token = counts.sum().item() / B
+    act = twell.packed_to_dense(packed, hl)
+    union = int((act != 0).any(dim=0).sum().item())
+
+    # algorithmic bytes per launch of the pack kernel: all of W_gate + x + slab words written
+    slab_bytes = 4 * (counts.clamp(max=31).sum().item() + counts.numel())
+    pack_bytes = 2 * d * hl + 2 * B * d + slab_bytes
+    peak, peak_kind = measured_peaks()
+    achieved = pack_bytes / (ms_pack * 1e-3) / 1e9
+    # whole-FFN algorithmic bytes (gate + active up/down rows + x, y + slab write/read)
+    ffn_bytes = 2 * d * hl + 2 * 2 * d * union + 2 * 2 * B * d + 2 * slab_bytes
+
+    result = {
+        "metric": METRIC, "value": B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"1.5B-shape sparse FFN stack decode: {L} layers, d_model {d}, "
+                               f"d_ff {args.d_ff}, batch {B}, gate density ~{DENSITY:.0%} "
+                               f"log-normal sigma {SKEW}",
+                   "layers": L, "d_model": d, "d_ff": args.d_ff, "batch": B,
+                   "d_ff_shard": [h0, h1], "parallelism": f"dff_shard{world}",
+                   "l2": "weights (2.8 GB) exceed L2; no flush needed",
+                   "nnz_per_token_last_layer": nnz_per_token,
+                   "active_union_last_layer": union,
+                   "ms_per_layer": ms_step / L,
+                   "ffn_algorithmic_gbs": ffn_bytes / (ms_step / L * 1e-3) / 1e9},
+        "roofline": {"bound": "hbm", "kernel": "twell_pack_kernel", "achieved": achieved,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None,
+                     "us_per_launch": ms_pack * 1e3, "algorithmic_bytes": pack_bytes},
+        "gpu_launches": args.steps * L * 2,
+        "clocks": clocks,
+    }
+
+    if not args.no_e2e:
+        result["e2e"] = run_e2e(args, layers, x, device, dist_on)
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(args, sample_layers=2, reps=3)
+    if rank == 0:
+        print(json.dumps(result))
+    if dist_on:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_e2e(args, layers, x, device, dist_on):
+    """Same stack through the public modules; host buffers in, host buffer out."""
+    import torch.distributed as dist
+    from sparser_faster_llms_b200 import twell
+    L, B, d = args.layers, args.batch, args.d_model
+    mods = [twell.TwELLGatedMLP(1000 + l, g, u, dn, preallocate_shared_hidden_state=True)
+            for l, (g, u, dn) in enumerate(layers)]
+    x_host = x.cpu().pin_memory()
+    y_host = torch.empty(L, B, d, dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty_like(x)
+    y_dev = torch.empty_like(x)
+
+    def step():
+        x_dev.copy_(x_host, non_blocking=True)
+        for l, m in enumerate(mods):
+            y = m(x_dev[l])
+            if dist_on:
+                dist.all_reduce(y)
+            y_dev[l].copy_(y)
+        y_host.copy_(y_dev, non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()
+
+    steps = max(5, args.steps // 2)
+    ms = time_replays(step, steps, 3, device, dist_on)
+    for m in mods:
+        m.destroy()
+    nbytes = L * B * d * 2
+    return {"value": B / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
+            "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
+            "api": "TwELLGatedMLP.forward per layer, eager launches, pinned host in/out"}
+
+
+# ----------------------------------------------------------------------------
+# CPU legs
+# ----------------------------------------------------------------------------
+def cpu_baseline(args, sample_layers, reps):
+    """Dense torch formulation of the FFN (the reference's CPU path,
+    sparse_models.py:343-351) on the host cores, bf16 weights, bounded sample."""
+    from oracle import ffn_oracle as fo
+    from sparser_faster_llms_b200 import synthetic
+    d, h, B = args.d_model, args.d_ff, args.batch
+    threads = torch.get_num_threads()
+    ffns = [synthetic.make_ffn(d, h, seed=50 + i, density=DENSITY, skew_sigma=SKEW)
+            for i in range(sample_layers)]
+    x = synthetic.make_tokens(B, d, seed=60)
+    ws = [(f.gate.float(), f.up.float(), f.down.float()) for f in ffns]
+    times = []
+    for r in range(reps + 1):
+        t0 = time.perf_counter()
+        for g, u, dn in ws:
+            fo.dense_ffn(x, g, u, dn)
+        times.append(time.perf_counter() - t0)
+    per_layer = statistics.median(times[1:]) / sample_layers
+    return {"value": B / (per_layer * args.layers), "unit": UNIT, "cores": threads,
+            "kind": "port", "ms_per_step": per_layer * args.layers * 1e3,
+            "sample": f"{sample_layers} of {args.layers} layers at batch {B}, fp32 torch dense "
+                      f"formula, median of {reps} reps, scaled to {args.layers} layers"}
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU torch formulation on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_layers = 4
+    reps = max(3, min(args.steps, 10))
+    base = cpu_baseline(args, sample_layers=sample_layers, reps=reps)
+    result = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"1.5B-shape sparse FFN stack decode: {args.layers} layers, "
+                               f"d_model {args.d_model}, d_ff {args.d_ff}, batch {args.batch}",
+                   "note": "reference CUDA kernels are sm_90a-only (WGMMA) and cannot run on "
+                           "sm_100; this arm times the reference's torch CPU formulation"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(result))
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); "
+                         "use --impl reference for the CPU arm")
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,102 @@
+/*
+ * b200_sparse_ffn.h - C ABI of the B200 (sm_100a) activation-sparse gated-FFN kernels.
+ *
+ * Every entry point takes raw device pointers, 64-bit sizes and a CUDA stream
+ * handle (a cudaStream_t passed as void*; NULL = the legacy default stream).
+ * No entry point allocates device memory, synchronises the host with the
+ * device, or keeps a pointer after it returns, unless its comment says so.
+ * All return 0 on success or a negative B200_E* code; the text of the last
+ * failure on the calling thread is available from b200_last_error().
+ *
+ * Layout conventions (TwELL layout of the reference, all row-major, bf16):
+ *   x     [M, D]   activations
+ *   gate, up, down [H, D]   (down = down_proj.weight transposed;
+ *                            reference: custom_models/sparse_testing_utils.py:23-34)
+ *   packed [M, (H/256) * (256/cf)] uint32 TwELL slabs
+ *          (reference spec: custom_models/twell_modules/twell.py:152-264)
+ * Constraints: D % 256 == 0, 256 <= D <= 8192; H % 256 == 0, H <= 65536;
+ * cf in {2,4,8}; pointers 16-byte aligned.  M >= 0 is unrestricted.
+ */
+#ifndef B200_SPARSE_FFN_H_
+#define B200_SPARSE_FFN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_OK 0
+#define B200_EINVAL (-1)      /* bad size / flag / compression factor          */
+#define B200_ENULL (-2)       /* a required pointer is NULL                    */
+#define B200_EALIGN (-3)      /* a pointer is not 16-byte aligned              */
+#define B200_EUNSUPPORTED (-4)/* shape outside the compiled range              */
+#define B200_ECUDA (-5)       /* CUDA runtime reported an error at launch      */
+#define B200_EWORKSPACE (-6)  /* caller-provided workspace is too small        */
+
+/* flags for the contraction entry points */
+#define B200_FLAG_HIGH_PRECISION 1u /* fp32 fma everywhere, h kept in fp32     */
+
+/* Library version (major*10000 + minor*100 + patch) and the sm arch it was built for. */
+int b200_version(void);
+int b200_built_for_sm(void);
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* b200_last_error(void);
+
+/*
+ * Gate projection + ReLU + TwELL pack:  packed = pack(relu(x @ w^T + bias)).
+ * Replaces matmul_sparse_out / run_d2t_layer
+ * (custom_models/twell_modules/twell.cpp:423-444, :583-601; kernel
+ * custom_models/twell_modules/matmul_d2t.cu:287-709).  `bias` ([H] fp32) may be
+ * NULL.  Each slab's word 0 receives the true count of positive
+ * pre-activations; words 1..min(count, 256/cf-1) receive col | bf16(value)<<16
+ * in ascending column order; the remaining words are left untouched.
+ */
+int b200_twell_pack(const void* x, const void* w, const float* bias, void* packed,
+                    int64_t M, int64_t D, int64_t H, int cf, void* stream);
+
+/*
+ * Gated TwELL -> dense contraction:
+ *   out[r,:] = sum over stored (j, g) of row r:  (g * (x[r,:] . up[j,:])) * down[j,:]
+ * Replaces matmul_gated_t2d_out and its flex / high-precision / in-place
+ * variants (custom_models/twell_modules/twell.cpp:499-539; kernels
+ * custom_models/twell_modules/matmul_gated_t2d.cu:17-594, :972-1541).
+ * `out` may alias `x` (in-place).  flags: B200_FLAG_HIGH_PRECISION.
+ */
+int b200_twell_gated_t2d(const void* x, const void* packed, const void* up,
+                         const void* down, void* out, int64_t M, int64_t D,
+                         int64_t H, int cf, uint32_t flags, void* stream);
+
+/*
+ * Non-gated TwELL -> dense down projection: out[r,:] = sum (v * down[j,:]).
+ * Replaces matmul_t2d_out (custom_models/twell_modules/twell.cpp:463-483;
+ * kernel custom_models/twell_modules/matmul_t2d.cu:15-113).  `num_splits` is
+ * accepted for signature compatibility (1, 2, 4 or 8) and does not change the
+ * result.
+ */
+int b200_twell_t2d(const void* packed, const void* down, void* out, int64_t M,
+                   int64_t D, int64_t H, int cf, int num_splits, void* stream);
+
+/*
+ * Fused gated MLP: pack(relu(x @ gate^T + bias)) into `packed`, then the gated
+ * contraction into `out` (may alias x).  Replaces TWELL_MLP::run_gated_mlp_layer*
+ * (custom_models/twell_modules/mlp_twell.cu:100-232).
+ */
+int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias,
+                         const void* up, const void* down, void* packed, void* out,
+                         int64_t M, int64_t D, int64_t H, int cf, uint32_t flags,
+                         void* stream);
+
+/*
+ * Fused non-gated MLP: pack(relu(x @ up^T)) then the down projection.
+ * Replaces TWELL_MLP::run_mlp_layer* (custom_models/twell_modules/mlp_twell.cu:73-98).
+ */
+int b200_twell_mlp(const void* x, const void* up, const void* down, void* packed,
+                   void* out, int64_t M, int64_t D, int64_t H, int cf,
+                   int num_splits, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_SPARSE_FFN_H_ */

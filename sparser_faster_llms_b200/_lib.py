@@ -1,0 +1,111 @@
+"""ctypes binding of ``libb200_sparse_ffn.so`` (declared in include/b200_sparse_ffn.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is
+raised.  Tensors are passed as raw device pointers, the stream is torch's
+current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int64, c_uint32, c_void_p
+from pathlib import Path
+
+import torch
+
+_PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = _PKG_DIR / "libb200_sparse_ffn.so"
+
+OK = 0
+FLAG_HIGH_PRECISION = 1
+
+_ERRORS = {
+    -1: "invalid argument",
+    -2: "null pointer",
+    -3: "misaligned pointer",
+    -4: "unsupported shape",
+    -5: "CUDA error",
+    -6: "workspace too small",
+}
+
+# name -> (restype, argtypes); mirrors include/b200_sparse_ffn.h
+_PROTOTYPES = {
+    "b200_version": (c_int, []),
+    "b200_built_for_sm": (c_int, []),
+    "b200_last_error": (c_char_p, []),
+    "b200_twell_pack": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                c_int64, c_int, c_void_p]),
+    "b200_twell_gated_t2d": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                     c_int64, c_int64, c_int, c_uint32, c_void_p]),
+    "b200_twell_t2d": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                               c_int, c_void_p]),
+    "b200_twell_gated_mlp": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_int64, c_int64, c_int64, c_int, c_uint32,
+                                     c_void_p]),
+    "b200_twell_mlp": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                               c_int64, c_int64, c_int, c_int, c_void_p]),
+}
+
+_LIB = None
+
+
+class B200Error(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, fn: str, code: int, text: str):
+        self.fn, self.code, self.text = fn, code, text
+        kind = _ERRORS.get(code, f"error {code}")
+        super().__init__(f"{fn} failed ({kind}): {text}")
+
+
+def load_library(path: str | Path | None = None) -> ctypes.CDLL:
+    """Load the shared library (once) and attach prototypes.  Raises if absent."""
+    global _LIB
+    if _LIB is not None and path is None:
+        return _LIB
+    lib_path = Path(path) if path is not None else LIB_PATH
+    if not lib_path.exists():
+        raise RuntimeError(
+            f"{lib_path} is missing: the sm_100a CUDA library has not been built. "
+            "Run `python -m sparser_faster_llms_b200.build` (needs nvcc). "
+            "There is no CPU or PyTorch fallback for these operators.")
+    lib = ctypes.CDLL(str(lib_path))
+    for name, (restype, argtypes) in _PROTOTYPES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = restype
+        fn.argtypes = argtypes
+    if path is None:
+        _LIB = lib
+    return lib
+
+
+def exported_names() -> list[str]:
+    return sorted(_PROTOTYPES)
+
+
+def last_error() -> str:
+    return load_library().b200_last_error().decode("utf-8", "replace")
+
+
+def check(fn_name: str, status: int) -> None:
+    if status != OK:
+        code = int(status)
+        if code in (-1, -2, -3, -4):
+            raise ValueError(str(B200Error(fn_name, code, last_error())))
+        raise B200Error(fn_name, code, last_error())
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def current_stream_handle(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def call(fn_name: str, device: torch.device, *args) -> None:
+    """Invoke ``fn_name(*args, stream)`` on ``device``'s current stream and raise on error."""
+    lib = load_library()
+    fn = getattr(lib, fn_name)
+    with torch.cuda.device(device):
+        status = fn(*args, current_stream_handle(device))
+    check(fn_name, status)

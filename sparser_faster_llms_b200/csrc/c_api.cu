@@ -1,0 +1,126 @@
+// extern "C" surface of the library: argument validation and dispatch.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace b200 {
+
+char* last_error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int twell_pack_small(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                     int64_t D, int64_t H, int cf, cudaStream_t stream);
+int t2d_cluster_size(int64_t M, int64_t D, int sm_count);
+int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
+                     const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf, int cs,
+                     cudaStream_t stream);
+
+// Number of SMs of the current device (cached per device ordinal).
+int sm_count() {
+  static int cache[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cache[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cache[dev] = n;
+  }
+  return cache[dev];
+}
+
+namespace {
+int check_ptr(const char* fn, const char* name, const void* p) {
+  if (p == nullptr) return fail(B200_ENULL, "%s: %s is NULL", fn, name);
+  if (!aligned16(p)) return fail(B200_EALIGN, "%s: %s is not 16-byte aligned", fn, name);
+  return B200_OK;
+}
+}  // namespace
+
+}  // namespace b200
+
+using namespace b200;
+
+#define B200_TRY(expr)        \
+  do {                        \
+    int rc__ = (expr);        \
+    if (rc__ != B200_OK) return rc__; \
+  } while (0)
+
+extern "C" {
+
+int b200_version(void) { return 100; }
+
+int b200_built_for_sm(void) { return 100; }
+
+const char* b200_last_error(void) { return last_error_buffer(); }
+
+int b200_twell_pack(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                    int64_t D, int64_t H, int cf, void* stream) {
+  const char* fn = "b200_twell_pack";
+  B200_TRY(check_dims(fn, M, D, H, cf));
+  if (M == 0) return B200_OK;
+  B200_TRY(check_ptr(fn, "x", x));
+  B200_TRY(check_ptr(fn, "w", w));
+  B200_TRY(check_ptr(fn, "packed", packed));
+  if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 3u))
+    return fail(B200_EALIGN, "%s: bias is not 4-byte aligned", fn);
+  return twell_pack_small(x, w, bias, packed, M, D, H, cf, static_cast<cudaStream_t>(stream));
+}
+
+int b200_twell_gated_t2d(const void* x, const void* packed, const void* up, const void* down,
+                         void* out, int64_t M, int64_t D, int64_t H, int cf, uint32_t flags,
+                         void* stream) {
+  const char* fn = "b200_twell_gated_t2d";
+  B200_TRY(check_dims(fn, M, D, H, cf));
+  if (flags & ~B200_FLAG_HIGH_PRECISION) return fail(B200_EINVAL, "%s: unknown flags 0x%x", fn, flags);
+  if (M == 0) return B200_OK;
+  B200_TRY(check_ptr(fn, "x", x));
+  B200_TRY(check_ptr(fn, "packed", packed));
+  B200_TRY(check_ptr(fn, "up", up));
+  B200_TRY(check_ptr(fn, "down", down));
+  B200_TRY(check_ptr(fn, "out", out));
+  const int cs = t2d_cluster_size(M, D, sm_count());
+  return twell_t2d_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, packed, up, down, out,
+                          M, D, H, cf, cs, static_cast<cudaStream_t>(stream));
+}
+
+int b200_twell_t2d(const void* packed, const void* down, void* out, int64_t M, int64_t D,
+                   int64_t H, int cf, int num_splits, void* stream) {
+  const char* fn = "b200_twell_t2d";
+  B200_TRY(check_dims(fn, M, D, H, cf));
+  if (num_splits != 1 && num_splits != 2 && num_splits != 4 && num_splits != 8)
+    return fail(B200_EINVAL, "%s: unsupported num_splits=%d (supported: 1/2/4/8)", fn, num_splits);
+  if (M == 0) return B200_OK;
+  B200_TRY(check_ptr(fn, "packed", packed));
+  B200_TRY(check_ptr(fn, "down", down));
+  B200_TRY(check_ptr(fn, "out", out));
+  const int cs = t2d_cluster_size(M, D, sm_count());
+  return twell_t2d_launch(false, false, nullptr, packed, nullptr, down, out, M, D, H, cf, cs,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias, const void* up,
+                         const void* down, void* packed, void* out, int64_t M, int64_t D,
+                         int64_t H, int cf, uint32_t flags, void* stream) {
+  B200_TRY(b200_twell_pack(x, gate, gate_bias, packed, M, D, H, cf, stream));
+  return b200_twell_gated_t2d(x, packed, up, down, out, M, D, H, cf, flags, stream);
+}
+
+int b200_twell_mlp(const void* x, const void* up, const void* down, void* packed, void* out,
+                   int64_t M, int64_t D, int64_t H, int cf, int num_splits, void* stream) {
+  B200_TRY(b200_twell_pack(x, up, nullptr, packed, M, D, H, cf, stream));
+  return b200_twell_t2d(packed, down, out, M, D, H, cf, num_splits, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,56 @@
+// Shared helpers for the sm_100a sparse-FFN kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/b200_sparse_ffn.h"
+
+namespace b200 {
+
+constexpr int kTileN = 256;  // TwELL tile width in neurons (reference: twell.py:152)
+
+// Thread-local text of the last failure, returned by b200_last_error().
+char* last_error_buffer();
+int fail(int code, const char* fmt, ...);
+
+inline bool aligned16(const void* p) {
+  return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+  return B200_OK;
+}
+
+// Validates the dimensions every entry point shares.
+inline int check_dims(const char* fn, int64_t M, int64_t D, int64_t H, int cf) {
+  if (cf != 2 && cf != 4 && cf != 8)
+    return fail(B200_EINVAL, "%s: compression_factor must be one of {8, 4, 2} (got %d)", fn, cf);
+  if (M < 0) return fail(B200_EINVAL, "%s: M must be >= 0 (got %lld)", fn, (long long)M);
+  if (M > (int64_t)1 << 30) return fail(B200_EUNSUPPORTED, "%s: M too large (%lld)", fn, (long long)M);
+  if (D < 256 || D > 8192 || D % 256)
+    return fail(B200_EUNSUPPORTED, "%s: D must be a multiple of 256 in [256, 8192] (got %lld)", fn,
+                (long long)D);
+  if (H < 256 || H > 65536 || H % 256)
+    return fail(B200_EUNSUPPORTED, "%s: H must be a multiple of 256 in [256, 65536] (got %lld)", fn,
+                (long long)H);
+  return B200_OK;
+}
+
+__device__ __forceinline__ uint32_t bf16_bits(float v) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+__device__ __forceinline__ uint32_t lanemask_lt() {
+  uint32_t m;
+  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+  return m;
+}
+
+}  // namespace b200

@@ -1,0 +1,162 @@
+"""Generate the golden fixtures from the reference's own torch implementation.
+
+Run in a container where the reference checkout is importable:
+
+    python tests/golden/make_golden.py --reference /path/to/sparser-faster-llms
+
+Writes ``tests/golden/*.npz``.  Sources of truth used (reference paths):
+
+* ``custom_models/sparse_models.py`` ``SparseMLP`` - inference logic (:343-351)
+  and training branch with the ``SparsityTracker`` l0 / l1 statistics
+  (:397-410, :148-181), plus autograd gradients of
+  ``sum(out * gout) + coeff * l1``;
+* ``custom_models/twell_modules/twell.py`` ``packed_to_dense`` (:215-264) - the
+  executable spec of the TwELL slab format.
+
+Weights are bf16-representable so that the CUDA kernels (bf16 storage) see
+exactly the same numbers as the fp32 reference run.
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+REPO = HERE.parent.parent
+sys.path.insert(0, str(REPO))
+
+from oracle import twell_format as tf  # noqa: E402
+from sparser_faster_llms_b200 import synthetic  # noqa: E402
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    return t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def sha(*tensors: torch.Tensor) -> str:
+    h = hashlib.sha256()
+    for t in tensors:
+        h.update(bits(t).tobytes())
+    return h.hexdigest()
+
+
+def build_sparse_mlp(ref, d, h, gate, up, down, bias, execution_logic):
+    from transformers import LlamaConfig
+    cfg = LlamaConfig(hidden_size=d, intermediate_size=h, mlp_bias=bias is not None)
+    tracker = ref.SparsityTracker(train_batch_size=1, max_seq_len=1,
+                                  per_device_train_batch_size=1, gated=True)
+    mlp = ref.SparseMLP(layer_idx=0, config=cfg, gated=True, tracker=tracker,
+                        execution_logic=execution_logic)
+    with torch.no_grad():
+        mlp.gate_proj.weight.copy_(gate.float())
+        mlp.up_proj.weight.copy_(up.float())
+        mlp.down_proj.weight.copy_(down.float().T)
+        if bias is not None:
+            mlp.gate_proj.bias.copy_(bias)
+            mlp.up_proj.bias.zero_()
+            mlp.down_proj.bias.zero_()
+    return mlp, tracker
+
+
+def case_small(ref, twell_ref, out: Path):
+    """Inputs stored in full: M=16, D=256, H=512."""
+    m, d, h = 16, 256, 512
+    ffn = synthetic.make_ffn(d, h, seed=11, density=0.05, skew_sigma=1.0)
+    x = synthetic.make_tokens(m, d, seed=12)
+    mlp, _ = build_sparse_mlp(ref, d, h, ffn.gate, ffn.up, ffn.down, None, "inference")
+    with torch.no_grad():
+        y32 = mlp(x.float()[None])[0]
+        y_bf16 = mlp.to(torch.bfloat16)(x[None])[0].float()
+    z = x.float() @ ffn.gate.float().T
+    fixtures = {"x": bits(x), "gate": bits(ffn.gate), "up": bits(ffn.up), "down": bits(ffn.down),
+                "y_fp32": y32.numpy(), "y_bf16_torch": y_bf16.numpy()}
+    for cf in (8, 4, 2):
+        packed = tf.pack_preactivations(z.numpy(), cf)
+        try:
+            dense = twell_ref.packed_to_dense(
+                torch.from_numpy(packed.view(np.int32)).view(torch.uint32), h,
+                compression_factor=cf)
+            fixtures[f"ref_dense_cf{cf}"] = bits(dense)
+            fixtures[f"ref_raises_cf{cf}"] = np.array(0)
+        except ValueError:
+            fixtures[f"ref_raises_cf{cf}"] = np.array(1)
+    np.savez_compressed(out / "small_gated.npz", **fixtures)
+
+
+def case_training(ref, out: Path):
+    """Training branch: l0 / l1 statistics and gradients. M=2x12, D=256, H=512."""
+    b, s, d, h = 2, 12, 256, 512
+    ffn = synthetic.make_ffn(d, h, seed=21, density=0.06, skew_sigma=0.5)
+    x = synthetic.make_tokens(b * s, d, seed=22).float().reshape(b, s, d)
+    gout = synthetic.make_tokens(b * s, d, seed=23, fold_bias=False).float().reshape(b, s, d)
+    coeff = 0.05
+    mlp, tracker = build_sparse_mlp(ref, d, h, ffn.gate, ffn.up, ffn.down, None, "training")
+    x = x.clone().requires_grad_(True)
+    tracker.start_forward_pass()
+    y = mlp(x)
+    l1, stats = tracker.finalize_forward_pass()
+    loss = (y * gout).sum() + coeff * l1
+    loss.backward()
+    np.savez_compressed(
+        out / "training_gated.npz",
+        seed_ffn=21, seed_x=22, seed_gout=23, coeff=coeff, b=b, s=s, d=d, h=h,
+        input_sha=np.array(sha(x.detach().reshape(-1, d), ffn.gate, ffn.up, ffn.down)),
+        y=y.detach().numpy(), l1=float(l1),
+        l0=float(stats["activation_l0/mean"]) if "activation_l0/mean" in stats else
+        float(list(v for k, v in stats.items() if k.startswith("activation_l0"))[0]),
+        dx=x.grad.numpy(), dgate=mlp.gate_proj.weight.grad.numpy(),
+        dup=mlp.up_proj.weight.grad.numpy(), ddown=mlp.down_proj.weight.grad.T.numpy().copy())
+
+
+def case_config1(ref, out: Path):
+    """Single-layer configuration: x [256, 1024] fp32 ~N(0,1), weights ~N(0, 0.02),
+    constant gate bias for about 2 % density.  Only outputs and an input hash are stored."""
+    m, d, h = 256, 1024, 4096
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn(m, d, generator=gen)
+    gate = (torch.randn(h, d, generator=gen) * 0.02).to(torch.bfloat16)
+    up = (torch.randn(h, d, generator=gen) * 0.02).to(torch.bfloat16)
+    down = (torch.randn(h, d, generator=gen) * 0.02).to(torch.bfloat16)
+    x = x.to(torch.bfloat16)
+    z0 = x.float() @ gate.float().T
+    shift = -float(torch.quantile(z0.flatten()[:: 7].float(), 0.98))
+    bias = torch.full((h,), shift)
+    mlp, _ = build_sparse_mlp(ref, d, h, gate, up, down, bias, "inference")
+    with torch.no_grad():
+        y = mlp(x.float()[None])[0]
+    z = z0 + shift
+    counts = tf.slab_counts(tf.pack_preactivations(z.numpy(), 2), 2)
+    np.savez_compressed(
+        out / "config1_gated.npz", m=m, d=d, h=h, seed=0, shift=shift,
+        input_sha=np.array(sha(x, gate, up, down)),
+        y_rows=y[:32].numpy(), y_norm=float(y.double().norm()),
+        counts=counts.astype(np.int16), density=float((z > 0).float().mean()))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    from custom_models import sparse_models as ref
+    import importlib.util
+    # twell.py imports torch.utils.cpp_extension only; it is safe to import on CPU.
+    spec = importlib.util.spec_from_file_location(
+        "ref_twell", Path(args.reference) / "custom_models/twell_modules/twell.py")
+    twell_ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(twell_ref)
+    torch.manual_seed(0)
+    case_small(ref, twell_ref, HERE)
+    case_training(ref, HERE)
+    case_config1(ref, HERE)
+    for p in sorted(HERE.glob("*.npz")):
+        print(p.name, p.stat().st_size)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,301 @@
+"""GPU parity of the TwELL pack and contraction kernels against the CPU oracle.
+
+Everything goes through the C-ABI library (ctypes) via the reference-compatible
+Python surface.  Integer outputs (counts, indices, value bits) are bit-exact on
+exact-arithmetic inputs and bit-exact outside a stated ambiguity band on
+Gaussian inputs; bf16 outputs are compared with stated tolerances.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ffn_oracle as fo
+from oracle import twell_format as tf
+from sparser_faster_llms_b200 import synthetic, twell
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+# Tolerances (relative L2 against an fp32 dense reference on the same bf16 inputs).
+# Mixed mode rounds every product and h to bf16 (about 2^-8 per operation, averaged
+# over the sum); high precision only rounds the stored gate value and the output.
+REL_L2_MIXED = 1.2e-2
+REL_L2_HP = 4e-3
+# Against the oracle fed the same slab only the fp32 summation order differs.
+REL_L2_SAME_SLAB = 2e-3
+
+
+def to_np_u32(t: torch.Tensor) -> np.ndarray:
+    return t.cpu().view(torch.int32).numpy().view(np.uint32)
+
+
+def gpu_pack(x, w, cf, bias=None):
+    packed = twell.allocate_packed_output(x.shape[0], w.shape[0], device=x.device,
+                                          compression_factor=cf)
+    if bias is None:
+        twell.matmul_sparse_out(x, w, packed, compression_factor=cf)
+    else:
+        twell.create_d2t_layer(9000, w, compression_factor=cf)
+        twell.set_d2t_layer_bias(9000, bias)
+        twell.run_d2t_layer(9000, x, packed)
+        twell.destroy_d2t_layer(9000)
+    torch.cuda.synchronize()
+    return packed
+
+
+@pytest.mark.parametrize("m,d,h", [(1, 256, 256), (7, 512, 1024), (8, 2048, 1024),
+                                   (32, 2048, 2048), (33, 1024, 512), (128, 256, 768),
+                                   (257, 512, 512), (16, 4096, 512), (5, 1024, 11008)])
+@pytest.mark.parametrize("cf", [8, 4, 2])
+def test_pack_exact_arithmetic_bit_exact(m, d, h, cf):
+    """Dyadic inputs: every fp32 partial sum is exact, so the slab bytes must be identical."""
+    x, gate, _, _ = synthetic.dyadic_case(m, d, h, seed=m + d + h)
+    want = tf.pack_preactivations(fo.gate_preactivation(x, gate).numpy(), cf)
+    got = to_np_u32(gpu_pack(x.to(DEV), gate.to(DEV), cf))
+    assert np.array_equal(tf.slab_counts(got, cf), tf.slab_counts(want, cf))
+    # kernel writes ascending order already: no sorting needed, unused words stay 0
+    assert np.array_equal(got, want)
+    assert (tf.slab_counts(want, cf) > 0).any()
+
+
+@pytest.mark.parametrize("m,d,h,density,skew", [(32, 2048, 8192, 0.02, 1.0),
+                                                (8, 1024, 4096, 0.02, 0.0),
+                                                (100, 512, 2048, 0.05, 1.0)])
+@pytest.mark.parametrize("cf", [8, 2])
+def test_pack_gaussian_bit_exact_outside_band(m, d, h, density, skew, cf):
+    ffn = synthetic.make_ffn(d, h, seed=3, density=density, skew_sigma=skew)
+    x = synthetic.make_tokens(m, d, seed=4)
+    amb, z64 = fo.ambiguity_mask(x, ffn.gate, rel=4e-6)
+    assert amb.float().mean() < 1e-4  # the band is a vanishing fraction
+    got = to_np_u32(gpu_pack(x.to(DEV), ffn.gate.to(DEV), cf))
+    w = tf.slab_words(cf)
+    # pattern: decode what the kernel stored (non-strict: overflowing slabs decode their prefix)
+    dense = tf.unpack_to_dense(got, h, cf, strict=False)
+    counts = tf.slab_counts(got, cf)
+    pos64 = (z64 > 0).numpy()
+    amb = amb.numpy()
+    # counts: equal to the fp64 count up to the ambiguous entries of that slab
+    c64 = pos64.reshape(m, h // 256, 256).sum(-1)
+    slack = amb.reshape(m, h // 256, 256).sum(-1)
+    assert (np.abs(counts - c64) <= slack).all()
+    ok_slab = np.repeat(counts <= w - 1, 256, axis=1)
+    sure = ~amb & ok_slab
+    assert np.array_equal((dense > 0)[sure], pos64[sure])
+    # values: RN bf16 of an fp32 accumulation; compare with bf16(fp32 oracle) up to 1 bf16 ulp
+    z32 = fo.gate_preactivation(x, ffn.gate).numpy()
+    sel = sure & pos64
+    want_bits = tf.f32_to_bf16_bits(z32)[sel].astype(np.int64)
+    got_bits = tf.f32_to_bf16_bits(dense)[sel].astype(np.int64)
+    assert np.abs(want_bits - got_bits).max() <= 1
+    assert (want_bits != got_bits).mean() < 0.02
+
+
+def test_pack_with_bias_matches_oracle():
+    m, d, h = 24, 1024, 2048
+    ffn = synthetic.make_ffn(d, h, seed=5, density=0.03, skew_sigma=1.0, fold_bias=False)
+    x = synthetic.make_tokens(m, d, seed=6, fold_bias=False)
+    z = fo.gate_preactivation(x, ffn.gate, ffn.gate_bias)
+    got = to_np_u32(gpu_pack(x.to(DEV), ffn.gate.to(DEV), 8, ffn.gate_bias.to(DEV)))
+    counts = tf.slab_counts(got, 8)
+    c32 = (z > 0).numpy().reshape(m, h // 256, 256).sum(-1)
+    assert np.abs(counts - c32).max() <= 1 and (counts != c32).mean() < 1e-2
+    assert 0.02 < counts.sum() / (m * h) < 0.045
+
+
+def _fresh_slab(x, ffn, cf, bias=None):
+    return fo.pack_gate(x, ffn.gate, bias, cf)
+
+
+@pytest.mark.parametrize("m,d,h", [(1, 2048, 8192), (8, 2048, 8192), (32, 2048, 8192),
+                                   (3, 256, 256), (40, 1024, 4096), (9, 4096, 1024),
+                                   (300, 512, 1024), (6, 768, 512), (2, 3584, 512)])
+@pytest.mark.parametrize("hp", [False, True])
+def test_gated_t2d_matches_oracle_on_same_slab(m, d, h, hp):
+    ffn = synthetic.make_ffn(d, h, seed=7, density=0.02, skew_sigma=1.0)
+    x = synthetic.make_tokens(m, d, seed=8)
+    packed = _fresh_slab(x, ffn, 8)
+    mo = min(m, 12)  # the loop oracle is slow: check a prefix of rows against it
+    want = fo.gated_t2d(x[:mo], packed[:mo], ffn.up, ffn.down, highest_precision=hp)
+    dense = fo.dense_ffn(x, ffn.gate, ffn.up, ffn.down)
+    xg = x.to(DEV)
+    pg = torch.from_numpy(packed.view(np.int32)).view(torch.uint32).to(DEV)
+    got = twell.matmul_gated_t2d(xg, pg, ffn.up.to(DEV), ffn.down.to(DEV), highest_precision=hp)
+    torch.cuda.synchronize()
+    got = got.float().cpu()
+    _, rel_same = fo.max_abs_and_rel_l2(got[:mo], want)
+    assert rel_same < REL_L2_SAME_SLAB, rel_same
+    max_abs, rel = fo.max_abs_and_rel_l2(got, dense)
+    assert rel < (REL_L2_HP if hp else REL_L2_MIXED), (max_abs, rel)
+
+
+@pytest.mark.parametrize("cf", [4, 2])
+def test_gated_t2d_other_slab_widths(cf):
+    m, d, h = 16, 1024, 2048
+    ffn = synthetic.make_ffn(d, h, seed=9, density=0.10, skew_sigma=0.5)
+    x = synthetic.make_tokens(m, d, seed=10)
+    packed = _fresh_slab(x, ffn, cf)
+    want = fo.gated_t2d(x[:6], packed[:6], ffn.up, ffn.down, compression_factor=cf)
+    pg = torch.from_numpy(packed.view(np.int32)).view(torch.uint32).to(DEV)
+    with pytest.raises(ValueError):
+        twell.matmul_gated_t2d(x.to(DEV), pg, ffn.up.to(DEV), ffn.down.to(DEV),
+                               compression_factor=cf)
+    got = twell.matmul_gated_t2d(x.to(DEV), pg, ffn.up.to(DEV), ffn.down.to(DEV),
+                                 compression_factor=cf, flex_kernels=True)
+    _, rel = fo.max_abs_and_rel_l2(got.float().cpu()[:6], want)
+    assert rel < REL_L2_SAME_SLAB
+
+
+def test_overflowing_slab_uses_stored_prefix_and_true_count():
+    """Dense rows overflow cf=8 slabs: count word keeps the true count, 31 entries stored."""
+    m, d, h = 4, 512, 512
+    ffn = synthetic.make_ffn(d, h, seed=13, density=0.4)
+    x = synthetic.make_tokens(m, d, seed=14)
+    got = to_np_u32(gpu_pack(x.to(DEV), ffn.gate.to(DEV), 8))
+    want = fo.pack_gate(x, ffn.gate, None, 8)
+    assert (tf.slab_counts(want, 8) > 31).all()
+    assert np.abs(tf.slab_counts(got, 8) - tf.slab_counts(want, 8)).max() <= 1
+    with pytest.raises(ValueError):
+        twell.packed_to_dense(torch.from_numpy(got.view(np.int32)).view(torch.uint32), h)
+    # the contraction consumes exactly the stored 31 entries per slab
+    pg = torch.from_numpy(want.view(np.int32)).view(torch.uint32).to(DEV)
+    y = twell.matmul_gated_t2d(x.to(DEV), pg, ffn.up.to(DEV), ffn.down.to(DEV))
+    ref = fo.gated_t2d(x, want, ffn.up, ffn.down)
+    _, rel = fo.max_abs_and_rel_l2(y.float().cpu(), ref)
+    assert rel < REL_L2_SAME_SLAB
+
+
+def test_t2d_non_gated_matches_oracle():
+    m, d, h = 20, 1024, 2048
+    ffn = synthetic.make_ffn(d, h, seed=15, density=0.03, skew_sigma=1.0)
+    x = synthetic.make_tokens(m, d, seed=16)
+    packed = fo.pack_gate(x, ffn.gate, None, 8)
+    want = fo.t2d(packed, ffn.down)
+    pg = torch.from_numpy(packed.view(np.int32)).view(torch.uint32).to(DEV)
+    for splits in (1, 2, 4, 8):
+        got = twell.matmul_t2d(pg, ffn.down.to(DEV), num_splits=splits)
+        _, rel = fo.max_abs_and_rel_l2(got.float().cpu(), want)
+        assert rel < REL_L2_SAME_SLAB
+    with pytest.raises(ValueError):
+        twell.matmul_t2d(pg, ffn.down.to(DEV), num_splits=3)
+    dense = fo.dense_mlp(x, ffn.gate, ffn.down)
+    _, rel = fo.max_abs_and_rel_l2(got.float().cpu(), dense)
+    assert rel < REL_L2_MIXED
+
+
+@pytest.mark.parametrize("inplace", [False, True])
+@pytest.mark.parametrize("shared", [False, True])
+@pytest.mark.parametrize("hp", [False, True])
+def test_gated_mlp_module_variants(inplace, shared, hp):
+    """TwELLGatedMLP built on CPU, moved with .to(device).to(dtype), all forward variants."""
+    b, s, d, h = 2, 9, 1024, 2048
+    ffn = synthetic.make_ffn(d, h, seed=17, density=0.02, skew_sigma=1.0, dtype=torch.float32)
+    x = synthetic.make_tokens(b * s, d, seed=18)
+    mod = twell.TwELLGatedMLP(layer_number=77, GATE=ffn.gate, UP=ffn.up, DOWN=ffn.down,
+                              inplace=inplace, preallocate_shared_hidden_state=shared,
+                              highest_precision=hp)
+    assert set(mod.state_dict().keys()) == {"GATE", "UP", "DOWN"}
+    mod = mod.eval().to(DEV).to(torch.bfloat16)
+    xin = x.to(DEV).reshape(b, s, d).clone()
+    y = mod(xin)
+    torch.cuda.synchronize()
+    assert y.shape == (b, s, d)
+    if inplace:
+        assert y.data_ptr() == xin.data_ptr()
+    dense = fo.dense_ffn(x, ffn.gate.bfloat16(), ffn.up.bfloat16(), ffn.down.bfloat16())
+    _, rel = fo.max_abs_and_rel_l2(y.float().cpu().reshape(-1, d), dense)
+    assert rel < (REL_L2_HP if hp else REL_L2_MIXED), rel
+    y2 = mod(x.to(DEV).reshape(b, s, d).clone())
+    assert torch.equal(y2, y)  # deterministic
+    mod.destroy()
+
+
+def test_non_gated_mlp_module():
+    m, d, h = 12, 512, 1024
+    ffn = synthetic.make_ffn(d, h, seed=19, density=0.03)
+    x = synthetic.make_tokens(m, d, seed=20)
+    mod = twell.TwELLMLP(layer_number=78, UP=ffn.gate, DOWN=ffn.down).to(DEV)
+    y = mod(x.to(DEV))
+    dense = fo.dense_mlp(x, ffn.gate, ffn.down)
+    _, rel = fo.max_abs_and_rel_l2(y.float().cpu(), dense)
+    assert rel < REL_L2_MIXED
+    mod.destroy()
+
+
+def test_linear_wrappers_and_packed_to_dense():
+    m, d, h = 10, 512, 1024
+    ffn = synthetic.make_ffn(d, h, seed=21, density=0.03)
+    x = synthetic.make_tokens(m, d, seed=22).to(DEV)
+    d2t = twell.D2TLinear(5, ffn.gate.to(DEV))
+    packed = d2t(x)
+    dense = twell.packed_to_dense(packed, h)
+    z = torch.relu(x.float() @ ffn.gate.to(DEV).float().T)
+    assert (dense.float() - z).abs().max() < 2e-2
+    gt = twell.GatedT2DLinear(ffn.up.to(DEV), ffn.down.to(DEV))
+    y = gt(x, packed)
+    ref = fo.dense_ffn(x.cpu(), ffn.gate, ffn.up, ffn.down)
+    _, rel = fo.max_abs_and_rel_l2(y.float().cpu(), ref)
+    assert rel < REL_L2_MIXED
+    t2d = twell.T2DLinear(ffn.down.to(DEV))
+    assert t2d(packed).shape == (m, d)
+    d2t.destroy()
+
+
+def test_bad_arguments_raise_python_exceptions():
+    x = torch.zeros(4, 512, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(512, 512, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        twell.matmul_sparse(x, w, compression_factor=3)
+    with pytest.raises(RuntimeError):
+        twell.matmul_sparse(x.float(), w)
+    with pytest.raises(ValueError):
+        twell.matmul_sparse(x, torch.zeros(300, 512, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        twell.matmul_sparse(x[:, ::2], w)  # non-contiguous
+    with pytest.raises(ValueError):
+        twell.matmul_sparse(torch.zeros(4, 128, device=DEV, dtype=torch.bfloat16),
+                            torch.zeros(256, 128, device=DEV, dtype=torch.bfloat16))  # D < 256
+    with pytest.raises(RuntimeError):
+        twell.run_d2t_layer(123456, x, twell.allocate_packed_output(4, 512, device=DEV))
+    # empty batch is a no-op
+    out = twell.matmul_sparse(x[:0], w)
+    assert out.shape == (0, 64)
+    torch.cuda.synchronize()
+
+
+def test_full_size_decode_shape_properties():
+    """1.5B-shape layer (D=2048, H=8192), batch 32, checked with size-independent properties
+    against torch on the GPU (fp32 matmul)."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    m, d, h = 32, 2048, 8192
+    ffn = synthetic.make_ffn(d, h, seed=30, density=0.02, skew_sigma=1.0, device=DEV)
+    x = synthetic.make_tokens(m, d, seed=31, device=DEV)
+    mod = twell.TwELLGatedMLP(0, ffn.gate, ffn.up, ffn.down)
+    y = mod(x)
+    packed = twell.matmul_sparse(x, ffn.gate)
+    z = x.float() @ ffn.gate.float().T
+    counts = packed.view(torch.int32)[:, ::32].long()
+    want = (z > 0).reshape(m, h // 256, 256).sum(-1)
+    assert (counts - want).abs().max() <= 1
+    assert (counts != want).float().mean() < 0.01
+    assert 0.01 < counts.sum().item() / (m * h) < 0.03
+    hid = torch.relu(z) * (x.float() @ ffn.up.float().T)
+    ref = hid @ ffn.down.float()
+    rel = ((y.float() - ref).norm() / ref.norm()).item()
+    assert rel < REL_L2_MIXED, rel
+    # linearity of the contraction in the gate values: doubling the slab values doubles y
+    p2 = packed.clone()
+    dense = twell.packed_to_dense(packed, h)
+    p2v = (dense * 2)
+    z2 = twell.matmul_gated_t2d(x, packed, ffn.up, ffn.down, highest_precision=True)
+    # rebuild a slab with doubled values through the pack kernel's own format
+    w = 32
+    slabs = packed.view(torch.int32).clone().view(m, h // 256, w)
+    vals = ((slabs[:, :, 1:] >> 16) & 0xFFFF).to(torch.int16).view(torch.bfloat16)
+    vals2 = (vals.float() * 2).to(torch.bfloat16).view(torch.int16).to(torch.int32) & 0xFFFF
+    slabs[:, :, 1:] = (slabs[:, :, 1:] & 0xFFFF) | (vals2 << 16)
+    y2 = twell.matmul_gated_t2d(x, slabs.view(m, -1).view(torch.uint32), ffn.up, ffn.down,
+                                highest_precision=True)
+    rel2 = ((y2.float() - 2 * z2.float()).norm() / (2 * z2.float()).norm()).item()
+    assert rel2 < 5e-3, rel2
+    del p2, p2v
+    mod.destroy()
