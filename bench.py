@@ -47,7 +47,7 @@ UNIT = "tokens/s"
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=32)
@@ -56,6 +56,8 @@ def parse():
     ap.add_argument("--d-ff", type=int, default=D_FF)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch eagerly instead of replaying a CUDA graph (for profilers)")
     return ap.parse_args()
 
 
@@ -85,7 +87,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "100"],
+                 "-i", str(self.index), "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -216,11 +218,15 @@ def run_ours(args):
     packed = torch.zeros(B, twell.packed_width(hl), device=device, dtype=torch.uint32)
     out = torch.empty(L, B, d, device=device, dtype=torch.bfloat16)
 
+    ws_buf = torch.zeros(int(_lib.load_library().b200_workspace_bytes()), dtype=torch.uint8,
+                         device=device)
+    ws = (ws_buf.data_ptr(), ws_buf.numel())
+
     def step():
         for l, (g, u, dn) in enumerate(layers):
             _lib.call("b200_twell_gated_mlp", device, x[l].data_ptr(), g.data_ptr(), None,
                       u.data_ptr(), dn.data_ptr(), packed.data_ptr(), out[l].data_ptr(),
-                      B, d, hl, 8, 0)
+                      B, d, hl, 8, 0, *ws)
             if dist_on:
                 dist.all_reduce(out[l])
 
@@ -232,13 +238,25 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    graph = capture(step, device)
-    ms_step = time_replays(graph.replay, args.steps, args.warmup, device, dist_on)
+    run_step = step if args.no_graph else capture(step, device).replay
+    ms_step = time_replays(run_step, args.steps, args.warmup, device, dist_on)
     clocks = sampler.stop() if rank == 0 else None
 
+    # dense GPU baseline: the same stack as three cuBLAS bf16 matmuls per layer (a reported
+    # comparison point, not part of the product path)
+    def dense_step():
+        for l, (g, u, dn) in enumerate(layers):
+            h = torch.relu(x[l] @ g.T) * (x[l] @ u.T)
+            torch.matmul(h, dn, out=out[l])
+
+    ms_dense = None
+    if not dist_on:
+        run_dense = dense_step if args.no_graph else capture(dense_step, device).replay
+        ms_dense = time_replays(run_dense, max(10, args.steps // 2), 3, device, False)
+
     # dominant kernel alone (per-launch time, CUDA events on the launching stream)
-    g_pack = capture(pack_only, device)
-    ms_pack = time_replays(g_pack.replay, max(10, args.steps // 2), 3, device, False) / L
+    run_pack = pack_only if args.no_graph else capture(pack_only, device).replay
+    ms_pack = time_replays(run_pack, max(10, args.steps // 2), 3, device, False) / L
     # statistics of the last slab for the byte model
     torch.cuda.synchronize(device)
     counts = packed.view(torch.int32)[:, ::32].long()
@@ -268,6 +286,7 @@ def run_ours(args):
                    "nnz_per_token_last_layer": nnz_per_token,
                    "active_union_last_layer": union,
                    "ms_per_layer": ms_step / L,
+                   "dense_cublas_bf16_ms_per_step": ms_dense,
                    "ffn_algorithmic_gbs": ffn_bytes / (ms_step / L * 1e-3) / 1e9},
         "roofline": {"bound": "hbm", "kernel": "twell_pack_kernel", "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
@@ -276,6 +295,33 @@ def run_ours(args):
         "gpu_launches": args.steps * L * 2,
         "clocks": clocks,
     }
+
+    # the other decode batch sizes of the configuration, measured the same way (shorter)
+    if not dist_on and not args.no_graph:
+        others = {}
+        for b2 in (1, 8):
+            if b2 >= B:
+                continue
+            xb = x[:, :b2].contiguous()
+
+            def step_b():
+                for l, (g, u, dn) in enumerate(layers):
+                    _lib.call("b200_twell_gated_mlp", device, xb[l].data_ptr(), g.data_ptr(), None,
+                              u.data_ptr(), dn.data_ptr(), packed.data_ptr(), out[l].data_ptr(),
+                              b2, d, hl, 8, 0, *ws)
+
+            def dense_b():
+                for l, (g, u, dn) in enumerate(layers):
+                    h = torch.relu(xb[l] @ g.T) * (xb[l] @ u.T)
+                    torch.matmul(h, dn, out=out[l, :b2])
+
+            ms_b = time_replays(capture(step_b, device).replay, max(10, args.steps // 2), 3,
+                                device, False)
+            ms_db = time_replays(capture(dense_b, device).replay, max(10, args.steps // 2), 3,
+                                 device, False)
+            others[str(b2)] = {"ms_per_step": ms_b, "tokens_per_s": b2 / (ms_b * 1e-3),
+                               "dense_cublas_bf16_ms_per_step": ms_db}
+        result["config"]["other_batches"] = others
 
     if not args.no_e2e:
         result["e2e"] = run_e2e(args, layers, x, device, dist_on)

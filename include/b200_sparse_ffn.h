@@ -45,6 +45,17 @@ int b200_built_for_sm(void);
 const char* b200_last_error(void);
 
 /*
+ * Optional workspace of the contraction entry points.  With few tokens (decode)
+ * the contraction spreads one token over the whole GPU and combines partial
+ * sums through global memory; that needs a caller-owned device buffer of at
+ * least b200_workspace_bytes() bytes, 16-byte aligned, zero-filled ONCE before
+ * its first use (the kernels leave it zeroed where it matters).  Calls that may
+ * overlap on the GPU (different streams) need different workspaces.  Passing
+ * NULL / 0 is always valid: one thread-block cluster per token is used instead.
+ */
+size_t b200_workspace_bytes(void);
+
+/*
  * Gate projection + ReLU + TwELL pack:  packed = pack(relu(x @ w^T + bias)).
  * Replaces matmul_sparse_out / run_d2t_layer
  * (custom_models/twell_modules/twell.cpp:423-444, :583-601; kernel
@@ -66,7 +77,8 @@ int b200_twell_pack(const void* x, const void* w, const float* bias, void* packe
  */
 int b200_twell_gated_t2d(const void* x, const void* packed, const void* up,
                          const void* down, void* out, int64_t M, int64_t D,
-                         int64_t H, int cf, uint32_t flags, void* stream);
+                         int64_t H, int cf, uint32_t flags, void* workspace,
+                         size_t workspace_bytes, void* stream);
 
 /*
  * Non-gated TwELL -> dense down projection: out[r,:] = sum (v * down[j,:]).
@@ -76,7 +88,8 @@ int b200_twell_gated_t2d(const void* x, const void* packed, const void* up,
  * result.
  */
 int b200_twell_t2d(const void* packed, const void* down, void* out, int64_t M,
-                   int64_t D, int64_t H, int cf, int num_splits, void* stream);
+                   int64_t D, int64_t H, int cf, int num_splits, void* workspace,
+                   size_t workspace_bytes, void* stream);
 
 /*
  * Fused gated MLP: pack(relu(x @ gate^T + bias)) into `packed`, then the gated
@@ -86,7 +99,7 @@ int b200_twell_t2d(const void* packed, const void* down, void* out, int64_t M,
 int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias,
                          const void* up, const void* down, void* packed, void* out,
                          int64_t M, int64_t D, int64_t H, int cf, uint32_t flags,
-                         void* stream);
+                         void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Fused non-gated MLP: pack(relu(x @ up^T)) then the down projection.
@@ -94,7 +107,8 @@ int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias
  */
 int b200_twell_mlp(const void* x, const void* up, const void* down, void* packed,
                    void* out, int64_t M, int64_t D, int64_t H, int cf,
-                   int num_splits, void* stream);
+                   int num_splits, void* workspace, size_t workspace_bytes,
+                   void* stream);
 
 #ifdef __cplusplus
 }

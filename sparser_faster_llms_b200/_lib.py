@@ -7,7 +7,7 @@ current CUDA stream.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_int, c_int64, c_uint32, c_void_p
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
 import torch
@@ -32,17 +32,19 @@ _PROTOTYPES = {
     "b200_version": (c_int, []),
     "b200_built_for_sm": (c_int, []),
     "b200_last_error": (c_char_p, []),
+    "b200_workspace_bytes": (c_size_t, []),
     "b200_twell_pack": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                 c_int64, c_int, c_void_p]),
     "b200_twell_gated_t2d": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
-                                     c_int64, c_int64, c_int, c_uint32, c_void_p]),
+                                     c_int64, c_int64, c_int, c_uint32, c_void_p, c_size_t,
+                                     c_void_p]),
     "b200_twell_t2d": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
-                               c_int, c_void_p]),
+                               c_int, c_void_p, c_size_t, c_void_p]),
     "b200_twell_gated_mlp": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_int64, c_int64, c_int64, c_int, c_uint32,
-                                     c_void_p]),
+                                     c_void_p, c_size_t, c_void_p]),
     "b200_twell_mlp": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
-                               c_int64, c_int64, c_int, c_int, c_void_p]),
+                               c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
 }
 
 _LIB = None
@@ -100,6 +102,26 @@ def ptr(t: torch.Tensor | None) -> int | None:
 
 def current_stream_handle(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def workspace(device: torch.device) -> tuple[int | None, int]:
+    """(pointer, bytes) of the zero-initialised contraction workspace of ``device``'s current
+    stream, created on first use.  During CUDA-graph capture no new workspace is created:
+    ``(None, 0)`` is returned and the kernels use their workspace-free shape."""
+    stream = torch.cuda.current_stream(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           stream.cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None, 0
+        nbytes = int(load_library().b200_workspace_bytes())
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws.data_ptr(), ws.numel()
 
 
 def call(fn_name: str, device: torch.device, *args) -> None:

@@ -20,10 +20,9 @@ int fail(int code, const char* fmt, ...) {
 
 int twell_pack_small(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                      int64_t D, int64_t H, int cf, cudaStream_t stream);
-int t2d_cluster_size(int64_t M, int64_t D, int sm_count);
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
-                     const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf, int cs,
-                     cudaStream_t stream);
+                     const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
+                     void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
 
 // Number of SMs of the current device (cached per device ordinal).
 int sm_count() {
@@ -43,6 +42,11 @@ namespace {
 int check_ptr(const char* fn, const char* name, const void* p) {
   if (p == nullptr) return fail(B200_ENULL, "%s: %s is NULL", fn, name);
   if (!aligned16(p)) return fail(B200_EALIGN, "%s: %s is not 16-byte aligned", fn, name);
+  return B200_OK;
+}
+int check_workspace(const char* fn, const void* ws) {
+  if (ws != nullptr && !aligned16(ws))
+    return fail(B200_EALIGN, "%s: workspace is not 16-byte aligned", fn);
   return B200_OK;
 }
 }  // namespace
@@ -65,6 +69,8 @@ int b200_built_for_sm(void) { return 100; }
 
 const char* b200_last_error(void) { return last_error_buffer(); }
 
+size_t b200_workspace_bytes(void) { return (size_t)1 << 20; }
+
 int b200_twell_pack(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                     int64_t D, int64_t H, int cf, void* stream) {
   const char* fn = "b200_twell_pack";
@@ -80,7 +86,7 @@ int b200_twell_pack(const void* x, const void* w, const float* bias, void* packe
 
 int b200_twell_gated_t2d(const void* x, const void* packed, const void* up, const void* down,
                          void* out, int64_t M, int64_t D, int64_t H, int cf, uint32_t flags,
-                         void* stream) {
+                         void* workspace, size_t workspace_bytes, void* stream) {
   const char* fn = "b200_twell_gated_t2d";
   B200_TRY(check_dims(fn, M, D, H, cf));
   if (flags & ~B200_FLAG_HIGH_PRECISION) return fail(B200_EINVAL, "%s: unknown flags 0x%x", fn, flags);
@@ -90,13 +96,15 @@ int b200_twell_gated_t2d(const void* x, const void* packed, const void* up, cons
   B200_TRY(check_ptr(fn, "up", up));
   B200_TRY(check_ptr(fn, "down", down));
   B200_TRY(check_ptr(fn, "out", out));
-  const int cs = t2d_cluster_size(M, D, sm_count());
+  B200_TRY(check_workspace(fn, workspace));
   return twell_t2d_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, packed, up, down, out,
-                          M, D, H, cf, cs, static_cast<cudaStream_t>(stream));
+                          M, D, H, cf, workspace, workspace_bytes, sm_count(),
+                          static_cast<cudaStream_t>(stream));
 }
 
 int b200_twell_t2d(const void* packed, const void* down, void* out, int64_t M, int64_t D,
-                   int64_t H, int cf, int num_splits, void* stream) {
+                   int64_t H, int cf, int num_splits, void* workspace, size_t workspace_bytes,
+                   void* stream) {
   const char* fn = "b200_twell_t2d";
   B200_TRY(check_dims(fn, M, D, H, cf));
   if (num_splits != 1 && num_splits != 2 && num_splits != 4 && num_splits != 8)
@@ -105,22 +113,27 @@ int b200_twell_t2d(const void* packed, const void* down, void* out, int64_t M, i
   B200_TRY(check_ptr(fn, "packed", packed));
   B200_TRY(check_ptr(fn, "down", down));
   B200_TRY(check_ptr(fn, "out", out));
-  const int cs = t2d_cluster_size(M, D, sm_count());
-  return twell_t2d_launch(false, false, nullptr, packed, nullptr, down, out, M, D, H, cf, cs,
+  B200_TRY(check_workspace(fn, workspace));
+  return twell_t2d_launch(false, false, nullptr, packed, nullptr, down, out, M, D, H, cf,
+                          workspace, workspace_bytes, sm_count(),
                           static_cast<cudaStream_t>(stream));
 }
 
 int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias, const void* up,
                          const void* down, void* packed, void* out, int64_t M, int64_t D,
-                         int64_t H, int cf, uint32_t flags, void* stream) {
+                         int64_t H, int cf, uint32_t flags, void* workspace,
+                         size_t workspace_bytes, void* stream) {
   B200_TRY(b200_twell_pack(x, gate, gate_bias, packed, M, D, H, cf, stream));
-  return b200_twell_gated_t2d(x, packed, up, down, out, M, D, H, cf, flags, stream);
+  return b200_twell_gated_t2d(x, packed, up, down, out, M, D, H, cf, flags, workspace,
+                              workspace_bytes, stream);
 }
 
 int b200_twell_mlp(const void* x, const void* up, const void* down, void* packed, void* out,
-                   int64_t M, int64_t D, int64_t H, int cf, int num_splits, void* stream) {
+                   int64_t M, int64_t D, int64_t H, int cf, int num_splits, void* workspace,
+                   size_t workspace_bytes, void* stream) {
   B200_TRY(b200_twell_pack(x, up, nullptr, packed, M, D, H, cf, stream));
-  return b200_twell_t2d(packed, down, out, M, D, H, cf, num_splits, stream);
+  return b200_twell_t2d(packed, down, out, M, D, H, cf, num_splits, workspace, workspace_bytes,
+                        stream);
 }
 
 }  // extern "C"

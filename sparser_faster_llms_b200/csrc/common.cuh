@@ -43,6 +43,20 @@ inline int check_dims(const char* fn, int64_t M, int64_t D, int64_t H, int cf) {
   return B200_OK;
 }
 
+// Raises a kernel's dynamic shared-memory limit once per device and size.
+template <typename Kernel>
+inline int ensure_dynamic_smem(Kernel kern, size_t bytes, size_t (&granted)[64], const char* what) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (bytes <= granted[dev]) return B200_OK;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess)
+    return fail(B200_ECUDA, "%s: cannot reserve %zu bytes of shared memory: %s", what, bytes,
+                cudaGetErrorString(e));
+  granted[dev] = bytes;
+  return B200_OK;
+}
+
 __device__ __forceinline__ uint32_t bf16_bits(float v) {
   return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
 }

@@ -1,15 +1,23 @@
 // TwELL -> dense contraction (gated up/down and plain down projection).
 //
-// One thread-block cluster per token.  The token's stored entries (over all
-// slabs) are numbered 0..n-1 and divided evenly over the cluster's CTAs and,
-// inside a CTA, over its warps.  For each entry (j, g) a warp
-//   * dots the token's x row (held in registers) with up[j, :]   (gated only),
-//   * forms h = g * u,
-//   * adds h * down[j, :] to a register accumulator spanning all D columns,
-// with 128-bit loads of the two weight rows.  Warp accumulators are summed in a
-// fixed order through shared memory, CTA sums through distributed shared memory,
-// so the result is deterministic.  At decode (M <= 32) the cluster spreads one
-// token over several SMs; at prefill one CTA per token keeps weight rows hot in L2.
+// A token's stored entries (over all slabs) are numbered 0..n-1 and divided
+// evenly over nc thread-block clusters of cs CTAs.  A CTA has one warp per
+// 256-column slice of d_model.  Entries are processed in batches; the up and
+// down rows of a whole batch are requested together (128-bit loads), so a batch
+// costs one memory round trip:
+//   pass A (gated only): warp s dots its slice of the token's x row (8 values per
+//           lane, in registers) with the same slice of up[j, :];
+//           slice sums meet in shared memory and give u, then h = g * u;
+//   pass B: warp s adds h * down[j, slice s] into 8 accumulators per lane - each
+//           warp owns its output columns, so no reduction inside the CTA.
+// The CTA pushes its column sums into the owning CTA of its cluster through
+// distributed shared memory; after one cluster barrier the owner adds the
+// cluster's contributions in rank order.  With one cluster per token it stores
+// bf16 directly.  With several (few tokens: spread one token over the whole
+// GPU) each owner writes its fp32 column sums to the workspace and bumps a
+// counter; the last owner to arrive adds the nc partial sums in cluster order,
+// stores bf16 and resets the counter.  Every sum has a fixed order: the result
+// is deterministic.
 //
 // Numerics follow the reference kernels: mixed mode rounds every product to
 // bf16 before the fp32 add and rounds h to bf16
@@ -17,8 +25,8 @@
 // high-precision mode uses fp32 fma throughout (matmul_gated_t2d.cu:389-441).
 // The reference's flex variants (:174-324, :466-594) differ only in how the slab
 // is read; this kernel reads any slab width.  The output row may alias the
-// input row (in-place variants, :972-1541): x is cached in registers before the
-// cluster barrier that precedes the first store.
+// input row (in-place variants, :972-1541): every CTA reads x before the
+// barrier / counter that precedes the first store.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -28,39 +36,56 @@ namespace cg = cooperative_groups;
 namespace b200 {
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
 constexpr int kMaxTiles = 256;  // H <= 65536
+constexpr int kChunk = 256;     // entries staged in shared memory at a time
+constexpr int kDepth = 8;       // entries per batch (row loads in flight per lane: 2x gated)
+constexpr int kStageWords = 4096;  // slab rows up to this many words are staged in shared memory
 
 __device__ __forceinline__ uint4 ldg_nc(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
 }
 
-// NI = D / 256.  Shared memory: entries[cap] | partial[kWarps][D] fp32.
+// NI = D / 256 = warps per CTA.
+// grid.x = M * nc * cs, cluster = cs.  ws_partial: [M][nc][D] fp32, ws_counter: [M][8] (nc > 1).
 template <int NI, bool GATED, bool HP>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(NI * 32)
 twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
                  const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
-                 __nv_bfloat16* out, int M, int tiles, int slab_w, int cs, int ent_cap) {
+                 __nv_bfloat16* out, int M, int tiles, int slab_w, int cs, int nc,
+                 float* ws_partial, unsigned int* ws_counter) {
   constexpr int D = NI * 256;
-  extern __shared__ __align__(16) unsigned char smem[];
-  uint32_t* entries = reinterpret_cast<uint32_t*>(smem);
-  float* partial = reinterpret_cast<float*>(smem + (size_t)ent_cap * sizeof(uint32_t));
+  constexpr int NTHREADS = NI * 32;
   __shared__ int tile_off[kMaxTiles + 1];
+  __shared__ uint32_t entries[kChunk];
+  __shared__ float usum[2][GATED ? kDepth : 1][GATED ? NI : 1];  // double-buffered per batch
+  __shared__ __align__(16) float inbox[D];  // [cs][D / cs]: column sums pushed by the cluster
+  __shared__ int is_last;
+  __shared__ __align__(16) uint32_t slab_s[kStageWords];
 
   cg::cluster_group cluster = cg::this_cluster();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int row = blockIdx.x / cs;
   const int crank = blockIdx.x % cs;
+  const int cidx = (blockIdx.x / cs) % nc;
+  const int row = blockIdx.x / (cs * nc);
   const uint32_t* prow = packed + (size_t)row * tiles * slab_w;
+  // Remote shared memory may only be touched once every CTA of the cluster runs:
+  // arrive now, wait right before the first remote store.
+  cluster.barrier_arrive();
 
-  // x row -> registers (lane owns columns it*256 + lane*8 .. +7).
-  uint4 xr[GATED ? NI : 1];
-  if (GATED) {
-#pragma unroll
-    for (int it = 0; it < NI; ++it)
-      xr[it] = *reinterpret_cast<const uint4*>(x + (size_t)row * D + it * 256 + lane * 8);
+  // This lane's 8 values of the x row (columns warp*256 + lane*8 .. +7).
+  uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+  if (GATED) xv = *reinterpret_cast<const uint4*>(x + (size_t)row * D + warp * 256 + lane * 8);
+
+  // One round trip brings the token's whole slab row on chip when it fits; the
+  // count words and entry words are then read from shared memory.
+  const int row_words = tiles * slab_w;
+  const bool staged = row_words <= kStageWords;
+  if (staged) {
+    for (int i = tid; i < row_words / 4; i += NTHREADS)
+      reinterpret_cast<uint4*>(slab_s)[i] = __ldg(reinterpret_cast<const uint4*>(prow) + i);
+    __syncthreads();
   }
+  const uint32_t* src = staged ? slab_s : prow;
 
   // Exclusive prefix of the per-slab entry counts (warp 0).
   if (warp == 0) {
@@ -69,7 +94,7 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
       const int tI = base + lane;
       int c = 0;
       if (tI < tiles) {
-        c = (int)prow[(size_t)tI * slab_w];
+        c = (int)src[(size_t)tI * slab_w];
         c = min(max(c, 0), slab_w - 1);
       }
       int inc = c;
@@ -85,146 +110,191 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
   }
   __syncthreads();
   const int n_total = tile_off[tiles];
-  const int per = (n_total + cs - 1) / cs;
-  const int lo = crank * per;
+  const int parts = cs * nc;
+  const int per = (n_total + parts - 1) / parts;
+  const int lo = (cidx * cs + crank) * per;
   const int hi = min(n_total, lo + per);
-  const int n_mine = max(hi - lo, 0);
 
-  // Gather this CTA's share of the entries.
-  for (int tI = warp; tI < tiles; tI += kWarps) {
-    const int o = tile_off[tI], c = tile_off[tI + 1] - o;
-    if (o + c <= lo || o >= hi) continue;
-    for (int s = lane; s < c; s += 32) {
-      const int k = o + s;
-      if (k >= lo && k < hi) entries[k - lo] = prow[(size_t)tI * slab_w + 1 + s];
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  int buf = 0;
+
+  const __nv_bfloat16* up_lane = up + warp * 256 + lane * 8;
+  const __nv_bfloat16* down_lane = down + warp * 256 + lane * 8;
+  const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+
+  for (int c0 = lo; c0 < hi; c0 += kChunk) {
+    const int n = min(kChunk, hi - c0);
+    // Gather this chunk's entry words: thread i finds entry c0 + i by binary search.
+    for (int i = tid; i < n; i += NTHREADS) {
+      const int k = c0 + i;
+      int a = 0, b = tiles;  // largest tile with tile_off[tile] <= k
+      while (b - a > 1) {
+        const int mid = (a + b) >> 1;
+        if (tile_off[mid] <= k) a = mid; else b = mid;
+      }
+      const uint32_t word = src[(size_t)a * slab_w + 1 + (k - tile_off[a])];
+      entries[i] = word;
     }
-  }
-  __syncthreads();
+    __syncthreads();
 
-  float acc[NI][8];
+    for (int e0 = 0; e0 < n; e0 += kDepth, buf ^= 1) {
+      uint4 uv[GATED ? kDepth : 1], dv[kDepth];
 #pragma unroll
-  for (int it = 0; it < NI; ++it)
+      for (int q = 0; q < kDepth; ++q) {
+        if (e0 + q < n) {
+          const size_t roff = (size_t)(entries[e0 + q] & 0xFFFFu) * D;
+          if (GATED) uv[q] = ldg_nc(up_lane + roff);
+          dv[q] = ldg_nc(down_lane + roff);
+        } else {
+          if (GATED) uv[q] = make_uint4(0u, 0u, 0u, 0u);
+          dv[q] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      if (GATED) {
+        // pass A: this warp's slice of the kDepth dot products (independent chains)
+        float u[kDepth];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[it][e] = 0.f;
-
-  for (int k = warp; k < n_mine; k += kWarps) {
-    const uint32_t word = entries[k];
-    const uint32_t j = word & 0xFFFFu;
-    const __nv_bfloat16 gval = __ushort_as_bfloat16((unsigned short)(word >> 16));
-    const __nv_bfloat16* drow = down + (size_t)j * D + lane * 8;
-    // The down row does not depend on u: fetch it before the dot product when
-    // the registers allow, so both rows are in flight together.
-    constexpr bool kPreload = NI <= 8;
-    uint4 dv[kPreload ? NI : 1];
-    if (kPreload) {
+        for (int q = 0; q < kDepth; ++q) {
+          const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&uv[q]);
+          float s = 0.f;
 #pragma unroll
-      for (int it = 0; it < NI; ++it) dv[it] = ldg_nc(drow + it * 256);
-    }
-
-    float hf;              // h as fp32 (high precision)
-    __nv_bfloat162 hb2;    // h as bf16 pair (mixed)
-    if (GATED) {
-      const __nv_bfloat16* urow = up + (size_t)j * D + lane * 8;
-      float u = 0.f;
+          for (int p = 0; p < 4; ++p) {
+            if (HP) {
+              const float2 wf = __bfloat1622float2(w2[p]), xf = __bfloat1622float2(x2[p]);
+              s = __fmaf_rn(wf.x, xf.x, s);
+              s = __fmaf_rn(wf.y, xf.y, s);
+            } else {
+              const float2 pf = __bfloat1622float2(__hmul2(x2[p], w2[p]));
+              s += pf.x;
+              s += pf.y;
+            }
+          }
+          u[q] = s;
+        }
 #pragma unroll
-      for (int it = 0; it < NI; ++it) {
-        const uint4 uv = ldg_nc(urow + it * 256);
-        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
-        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xr[it]);
+        for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          if (HP) {
-            const float2 wf = __bfloat1622float2(w2[p]), xf = __bfloat1622float2(x2[p]);
-            u = __fmaf_rn(wf.x, xf.x, u);
-            u = __fmaf_rn(wf.y, xf.y, u);
-          } else {
-            const float2 pf = __bfloat1622float2(__hmul2(x2[p], w2[p]));
-            u += pf.x;
-            u += pf.y;
+          for (int q = 0; q < kDepth; ++q) u[q] += __shfl_xor_sync(0xffffffffu, u[q], o);
+        }
+        if (lane == 0) {
+#pragma unroll
+          for (int q = 0; q < kDepth; ++q) usum[buf][q][warp] = u[q];
+        }
+        __syncthreads();
+      }
+      // h of entry e0 + lane (fixed-order sum over the slices), then broadcast.
+      float h_lane = 0.f;
+      if (lane < kDepth && e0 + lane < n) {
+        const __nv_bfloat16 gval = __ushort_as_bfloat16((unsigned short)(entries[e0 + lane] >> 16));
+        if (GATED) {
+          float s = 0.f;
+#pragma unroll
+          for (int sI = 0; sI < NI; ++sI) s += usum[buf][lane][sI];
+          h_lane = HP ? __bfloat162float(gval) * s
+                      : __bfloat162float(__hmul(gval, __float2bfloat16_rn(s)));
+        } else {
+          h_lane = __bfloat162float(gval);
+        }
+      }
+      // pass B: column-sliced down projection (padding entries have h = 0, row = 0)
+#pragma unroll
+      for (int q = 0; q < kDepth; ++q) {
+        const float h = __shfl_sync(0xffffffffu, h_lane, q);
+        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&dv[q]);
+        if (HP) {
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const float2 wf = __bfloat1622float2(w2[p]);
+            acc[2 * p] = __fmaf_rn(wf.x, h, acc[2 * p]);
+            acc[2 * p + 1] = __fmaf_rn(wf.y, h, acc[2 * p + 1]);
+          }
+        } else {
+          const __nv_bfloat162 hb2 = __float2bfloat162_rn(h);  // h is bf16-representable
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const float2 pf = __bfloat1622float2(__hmul2(hb2, w2[p]));
+            acc[2 * p] += pf.x;
+            acc[2 * p + 1] += pf.y;
           }
         }
       }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) u += __shfl_xor_sync(0xffffffffu, u, o);
-      if (HP) {
-        hf = __bfloat162float(gval) * u;
-      } else {
-        hb2 = __bfloat162bfloat162(__hmul(gval, __float2bfloat16_rn(u)));
-      }
-    } else {
-      hf = __bfloat162float(gval);
-      hb2 = __bfloat162bfloat162(gval);
     }
-
-#pragma unroll
-    for (int it = 0; it < NI; ++it) {
-      uint4 dcur;
-      if (kPreload) dcur = dv[it]; else dcur = ldg_nc(drow + it * 256);
-      const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&dcur);
-#pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        if (HP) {
-          const float2 wf = __bfloat1622float2(w2[p]);
-          acc[it][2 * p] = __fmaf_rn(wf.x, hf, acc[it][2 * p]);
-          acc[it][2 * p + 1] = __fmaf_rn(wf.y, hf, acc[it][2 * p + 1]);
-        } else {
-          const float2 pf = __bfloat1622float2(__hmul2(hb2, w2[p]));
-          acc[it][2 * p] += pf.x;
-          acc[it][2 * p + 1] += pf.y;
-        }
-      }
-    }
+    __syncthreads();  // entries are rewritten by the next chunk
   }
 
-  // Warp accumulators -> shared memory, fixed-order sum over warps.
-#pragma unroll
-  for (int it = 0; it < NI; ++it) {
-    float* p = partial + (size_t)warp * D + it * 256 + lane * 8;
-    *reinterpret_cast<float4*>(p) = make_float4(acc[it][0], acc[it][1], acc[it][2], acc[it][3]);
-    *reinterpret_cast<float4*>(p + 4) = make_float4(acc[it][4], acc[it][5], acc[it][6], acc[it][7]);
-  }
-  __syncthreads();
-  for (int c = tid; c < D; c += kThreads) {
-    float s = partial[c];
-#pragma unroll
-    for (int wI = 1; wI < kWarps; ++wI) s += partial[(size_t)wI * D + c];
-    partial[c] = s;  // column c is read and written by this thread only
+  // Push this CTA's column sums to the owners: CTA r owns columns [r*cols, (r+1)*cols)
+  // and receives rank q's contribution in inbox[q*cols .. (q+1)*cols).
+  const int cols = D / cs;
+  cluster.barrier_wait();
+  {
+    const int c = warp * 256 + lane * 8;  // first of this lane's 8 columns
+    const int owner = c / cols, off = c - owner * cols;
+    float* dst = cluster.map_shared_rank(inbox, owner) + (size_t)crank * cols + off;
+    *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
   cluster.sync();
 
-  // Cluster reduction: CTA r finishes columns [r*D/cs, (r+1)*D/cs).
-  const int cols = D / cs;
-  for (int c = tid * 2; c < cols; c += kThreads * 2) {
-    const int col = crank * cols + c;
+  __nv_bfloat16* orow = out + (size_t)row * D + crank * cols;
+  if (nc == 1) {
+    for (int c = tid * 2; c < cols; c += NTHREADS * 2) {
+      float s0 = 0.f, s1 = 0.f;
+      for (int q = 0; q < cs; ++q) {
+        const float2 v = *reinterpret_cast<const float2*>(inbox + (size_t)q * cols + c);
+        s0 += v.x;
+        s1 += v.y;
+      }
+      *reinterpret_cast<__nv_bfloat162*>(orow + c) = __floats2bfloat162_rn(s0, s1);
+    }
+    return;
+  }
+
+  // Several clusters per token: publish this cluster's column sums, last arrival finishes.
+  float* my_part = ws_partial + ((size_t)row * nc + cidx) * D + crank * cols;
+  for (int c = tid * 2; c < cols; c += NTHREADS * 2) {
     float s0 = 0.f, s1 = 0.f;
-    for (int r = 0; r < cs; ++r) {
-      const float* peer = cluster.map_shared_rank(partial, r);
-      const float2 v = *reinterpret_cast<const float2*>(peer + col);
+    for (int q = 0; q < cs; ++q) {
+      const float2 v = *reinterpret_cast<const float2*>(inbox + (size_t)q * cols + c);
       s0 += v.x;
       s1 += v.y;
     }
-    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)row * D + col) = __floats2bfloat162_rn(s0, s1);
+    __stcg(reinterpret_cast<float2*>(my_part + c), make_float2(s0, s1));
   }
-  cluster.sync();  // keep shared memory alive until every peer has read it
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned int old = atomicAdd(&ws_counter[row * 8 + crank], 1u);
+    is_last = (old == (unsigned int)(nc - 1));
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const float* tok_part = ws_partial + (size_t)row * nc * D + crank * cols;
+  for (int c = tid * 2; c < cols; c += NTHREADS * 2) {
+    float s0 = 0.f, s1 = 0.f;
+    for (int q = 0; q < nc; ++q) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(tok_part + (size_t)q * D + c));
+      s0 += v.x;
+      s1 += v.y;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(orow + c) = __floats2bfloat162_rn(s0, s1);
+  }
+  if (tid == 0) ws_counter[row * 8 + crank] = 0u;  // ready for the next launch
 }
 
 template <int NI, bool GATED, bool HP>
 int launch_t2d(const void* x, const void* packed, const void* up, const void* down, void* out,
-               int64_t M, int64_t H, int cf, int cs, cudaStream_t stream) {
-  constexpr int D = NI * 256;
+               int64_t M, int64_t H, int cf, int cs, int nc, float* ws_partial,
+               unsigned int* ws_counter, cudaStream_t stream) {
   const int slab_w = kTileN / cf;
   const int tiles = (int)(H / kTileN);
-  // Worst-case entries one CTA may hold: its share of a row that is full everywhere.
-  const int64_t full = (int64_t)tiles * (slab_w - 1);
-  const int ent_cap = (int)(((full + cs - 1) / cs + 3) & ~(int64_t)3);
-  const size_t smem = (size_t)ent_cap * 4 + (size_t)kWarps * D * sizeof(float);
   auto kern = twell_t2d_kernel<NI, GATED, HP>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return fail(B200_ECUDA, "twell_t2d: smem attribute (%zu B): %s", smem, cudaGetErrorString(e));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(M * cs), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem;
+  cfg.gridDim = dim3((unsigned)(M * nc * cs), 1, 1);
+  cfg.blockDim = dim3(NI * 32, 1, 1);
+  cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -233,50 +303,74 @@ int launch_t2d(const void* x, const void* packed, const void* up, const void* do
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kern, reinterpret_cast<const __nv_bfloat16*>(x),
-                         reinterpret_cast<const uint32_t*>(packed),
-                         reinterpret_cast<const __nv_bfloat16*>(up),
-                         reinterpret_cast<const __nv_bfloat16*>(down),
-                         reinterpret_cast<__nv_bfloat16*>(out), (int)M, tiles, slab_w, cs, ent_cap);
+  cudaError_t e = cudaLaunchKernelEx(
+      &cfg, kern, reinterpret_cast<const __nv_bfloat16*>(x),
+      reinterpret_cast<const uint32_t*>(packed), reinterpret_cast<const __nv_bfloat16*>(up),
+      reinterpret_cast<const __nv_bfloat16*>(down), reinterpret_cast<__nv_bfloat16*>(out), (int)M,
+      tiles, slab_w, cs, nc, ws_partial, ws_counter);
   if (e != cudaSuccess) return fail(B200_ECUDA, "twell_t2d: launch: %s", cudaGetErrorString(e));
   return B200_OK;
 }
 
 template <bool GATED, bool HP>
 int dispatch_ni(int ni, const void* x, const void* packed, const void* up, const void* down,
-                void* out, int64_t M, int64_t H, int cf, int cs, cudaStream_t stream) {
+                void* out, int64_t M, int64_t H, int cf, int cs, int nc, float* ws_partial,
+                unsigned int* ws_counter, cudaStream_t stream) {
   switch (ni) {
-#define B200_CASE(N) \
-  case N: return launch_t2d<N, GATED, HP>(x, packed, up, down, out, M, H, cf, cs, stream);
+#define B200_CASE(N)                                                                           \
+  case N:                                                                                      \
+    return launch_t2d<N, GATED, HP>(x, packed, up, down, out, M, H, cf, cs, nc, ws_partial,   \
+                                    ws_counter, stream);
     B200_CASE(1) B200_CASE(2) B200_CASE(3) B200_CASE(4) B200_CASE(5) B200_CASE(6) B200_CASE(7)
-    B200_CASE(8) B200_CASE(10) B200_CASE(12) B200_CASE(14) B200_CASE(16)
+    B200_CASE(8) B200_CASE(9) B200_CASE(10) B200_CASE(11) B200_CASE(12) B200_CASE(13)
+    B200_CASE(14) B200_CASE(15) B200_CASE(16)
 #undef B200_CASE
     default:
-      return fail(B200_EUNSUPPORTED,
-                  "twell_t2d: D = %d is not compiled (supported: 256*k for k in 1..8,10,12,14,16)",
+      return fail(B200_EUNSUPPORTED, "twell_t2d: D = %d is not compiled (supported: 256..4096)",
                   ni * 256);
   }
 }
 
 }  // namespace
 
-// Cluster size: spread a token over several SMs while there are fewer tokens
-// than SMs, keeping D divisible by 2*cs.
-int t2d_cluster_size(int64_t M, int64_t D, int sm_count) {
+// Workspace layout: [kCounterWords counters][fp32 partial sums].
+constexpr size_t kCounterWords = 4096;
+
+// Launch shape.  cs: CTAs per cluster (D / cs must stay a multiple of 8 columns).
+// nc: clusters per token - more than one only when there are few tokens and the
+// caller's workspace can hold the partial sums.
+void t2d_shape(int64_t M, int64_t D, int sm_count, size_t workspace_bytes, int* cs_out,
+               int* nc_out) {
   int cs = 1;
-  while (cs < 8 && M * cs * 2 <= (int64_t)sm_count * 2 && (D / (cs * 2)) % 2 == 0) cs *= 2;
-  return cs;
+  while (cs < 8 && M * cs * 2 <= (int64_t)sm_count * 2 && (D / (cs * 2)) % 8 == 0) cs *= 2;
+  int nc = 1;
+  if (workspace_bytes > kCounterWords * 4 && M * 8 <= (int64_t)kCounterWords) {
+    const int64_t cap_floats = (int64_t)((workspace_bytes - kCounterWords * 4) / 4);
+    int64_t want = ((int64_t)sm_count * 2) / (M * cs);  // about two CTAs per SM in total
+    if (want > 32) want = 32;
+    while (want > 1 && M * want * D > cap_floats) --want;
+    if (want > 1) nc = (int)want;
+  }
+  *cs_out = cs;
+  *nc_out = nc;
 }
 
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
-                     const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf, int cs,
-                     cudaStream_t stream) {
+                     const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
+                     void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+  int cs = 1, nc = 1;
+  t2d_shape(M, D, sm_count, workspace != nullptr ? workspace_bytes : 0, &cs, &nc);
+  unsigned int* counters = reinterpret_cast<unsigned int*>(workspace);
+  float* partial = workspace ? reinterpret_cast<float*>(counters + kCounterWords) : nullptr;
   const int ni = (int)(D / 256);
   if (gated) {
-    return hp ? dispatch_ni<true, true>(ni, x, packed, up, down, out, M, H, cf, cs, stream)
-              : dispatch_ni<true, false>(ni, x, packed, up, down, out, M, H, cf, cs, stream);
+    return hp ? dispatch_ni<true, true>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
+                                        counters, stream)
+              : dispatch_ni<true, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
+                                         counters, stream);
   }
-  return dispatch_ni<false, false>(ni, x, packed, up, down, out, M, H, cf, cs, stream);
+  return dispatch_ni<false, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
+                                   counters, stream);
 }
 
 }  // namespace b200

@@ -81,8 +81,11 @@ def dyadic_case(m: int, d_model: int, d_ff: int, *, seed: int = 0, device="cpu")
     x = torch.randint(-2, 3, (m, d_model), generator=gen).float() / 2
     gate = torch.randint(-4, 5, (d_ff, d_model), generator=gen).float() / 64
     # shift towards sparsity: most pre-activations negative
-    gate[:, 0] = -2.0
-    x[:, 0] = torch.randint(2, 4, (m,), generator=gen).float() / 2
+    # feature 0 carries a negative shift of about two standard deviations of the
+    # remaining sum (a multiple of 1/2, exactly representable)
+    sigma = math.sqrt((d_model - 1) * 0.5 * (60.0 / 9.0) / 4096.0)
+    gate[:, 0] = -max(0.5, round(4.0 * sigma) / 2.0)
+    x[:, 0] = 1.0
     up = torch.randint(-4, 5, (d_ff, d_model), generator=gen).float() / 64
     down = torch.randint(-4, 5, (d_ff, d_model), generator=gen).float() / 64
     bf = torch.bfloat16

@@ -265,7 +265,8 @@ def _native_gated_t2d(IN_dense, GATE_packed, UP, DOWN, OUT, highest_precision, c
     dev = _same_device(IN_dense, GATE_packed, UP, DOWN, OUT)
     flags = _lib.FLAG_HIGH_PRECISION if highest_precision else 0
     _lib.call("b200_twell_gated_t2d", dev, IN_dense.data_ptr(), GATE_packed.data_ptr(),
-              UP.data_ptr(), DOWN.data_ptr(), OUT.data_ptr(), m, d, h, cf, flags)
+              UP.data_ptr(), DOWN.data_ptr(), OUT.data_ptr(), m, d, h, cf, flags,
+              *_lib.workspace(dev))
 
 
 def _native_t2d(IN_packed, DOWN, OUT, num_splits, cf=8) -> None:
@@ -278,7 +279,7 @@ def _native_t2d(IN_packed, DOWN, OUT, num_splits, cf=8) -> None:
     _check_packed(IN_packed, m, h, cf, "IN_packed")
     dev = _same_device(IN_packed, DOWN, OUT)
     _lib.call("b200_twell_t2d", dev, IN_packed.data_ptr(), DOWN.data_ptr(), OUT.data_ptr(),
-              m, d, h, cf, int(num_splits))
+              m, d, h, cf, int(num_splits), *_lib.workspace(dev))
 
 
 # layer_number -> {"B": weight, "cf": int, "bias": tensor | None, "m": int | None}
@@ -439,7 +440,7 @@ def _gated_mlp(layer_number, A, UP, DOWN, C_packed, OUT, highest_precision, cf) 
     flags = _lib.FLAG_HIGH_PRECISION if highest_precision else 0
     _lib.call("b200_twell_gated_mlp", dev, A.data_ptr(), GATE.data_ptr(),
               _lib.ptr(entry["bias"]), UP.data_ptr(), DOWN.data_ptr(), C_packed.data_ptr(),
-              OUT.data_ptr(), m, d, h, cf, flags)
+              OUT.data_ptr(), m, d, h, cf, flags, *_lib.workspace(dev))
     entry["m"] = m
 
 
@@ -455,7 +456,8 @@ def _plain_mlp(layer_number, A, DOWN, C_packed, OUT, num_splits) -> None:
     _check_packed(C_packed, m, h, entry["cf"], "C_packed")
     dev = _same_device(A, UP, DOWN, C_packed, OUT)
     _lib.call("b200_twell_mlp", dev, A.data_ptr(), UP.data_ptr(), DOWN.data_ptr(),
-              C_packed.data_ptr(), OUT.data_ptr(), m, d, h, entry["cf"], int(num_splits))
+              C_packed.data_ptr(), OUT.data_ptr(), m, d, h, entry["cf"], int(num_splits),
+              *_lib.workspace(dev))
     entry["m"] = m
 
 

@@ -50,14 +50,15 @@ def test_argument_validation_happens_before_any_cuda_call(lib):
     # null and misaligned pointers
     assert lib.b200_twell_pack(None, p16, None, p16, 4, 256, 256, 8, None) == -2
     assert lib.b200_twell_pack(p16 + 2, p16, None, p16, 4, 256, 256, 8, None) == -3
-    assert lib.b200_twell_gated_t2d(p16, p16, None, p16, p16, 4, 256, 256, 8, 0, None) == -2
-    assert lib.b200_twell_gated_t2d(p16, p16, p16, p16, p16, 4, 256, 256, 8, 0x80, None) == -1
-    assert lib.b200_twell_t2d(p16, p16, p16, 4, 256, 256, 8, 3, None) == -1
+    assert lib.b200_twell_gated_t2d(p16, p16, None, p16, p16, 4, 256, 256, 8, 0, None, 0, None) == -2
+    assert lib.b200_twell_gated_t2d(p16, p16, p16, p16, p16, 4, 256, 256, 8, 0x80, None, 0, None) == -1
+    assert lib.b200_twell_t2d(p16, p16, p16, 4, 256, 256, 8, 3, None, 0, None) == -1
     # M == 0 is a successful no-op and needs no pointers
     assert lib.b200_twell_pack(None, None, None, None, 0, 256, 256, 8, None) == 0
     assert lib.b200_twell_gated_mlp(None, None, None, None, None, None, None, 0, 256, 256, 8, 0,
-                                    None) == 0
-    assert lib.b200_twell_mlp(None, None, None, None, None, 0, 256, 256, 8, 2, None) == 0
+                                    None, 0, None) == 0
+    assert lib.b200_twell_mlp(None, None, None, None, None, 0, 256, 256, 8, 2, None, 0, None) == 0
+    assert lib.b200_workspace_bytes() >= 1 << 20
 
 
 def test_missing_library_fails_loudly(tmp_path):

@@ -55,7 +55,8 @@ def test_pack_exact_arithmetic_bit_exact(m, d, h, cf):
     assert np.array_equal(tf.slab_counts(got, cf), tf.slab_counts(want, cf))
     # kernel writes ascending order already: no sorting needed, unused words stay 0
     assert np.array_equal(got, want)
-    assert (tf.slab_counts(want, cf) > 0).any()
+    if m * h >= 8192:
+        assert (tf.slab_counts(want, cf) > 0).any()
 
 
 @pytest.mark.parametrize("m,d,h,density,skew", [(32, 2048, 8192, 0.02, 1.0),
@@ -299,3 +300,26 @@ def test_full_size_decode_shape_properties():
     assert rel2 < 5e-3, rel2
     del p2, p2v
     mod.destroy()
+
+
+@pytest.mark.parametrize("m", [1, 2, 8])
+def test_workspace_and_workspace_free_paths_agree(m):
+    """Few tokens: the multi-cluster path (needs the workspace) against one cluster per token."""
+    from sparser_faster_llms_b200 import _lib
+    d, h = 2048, 8192
+    ffn = synthetic.make_ffn(d, h, seed=40, density=0.02, skew_sigma=1.0, device=DEV)
+    x = synthetic.make_tokens(m, d, seed=41, device=DEV)
+    packed = twell.matmul_sparse(x, ffn.gate)
+    ws = torch.zeros(int(_lib.load_library().b200_workspace_bytes()), dtype=torch.uint8, device=DEV)
+    outs = []
+    for wsp, wsb in ((None, 0), (ws.data_ptr(), ws.numel()), (ws.data_ptr(), ws.numel())):
+        y = torch.empty_like(x)
+        _lib.call("b200_twell_gated_t2d", torch.device(DEV), x.data_ptr(), packed.data_ptr(),
+                  ffn.up.data_ptr(), ffn.down.data_ptr(), y.data_ptr(), m, d, h, 8, 0, wsp, wsb)
+        outs.append(y.float())
+    torch.cuda.synchronize()
+    assert torch.equal(outs[1], outs[2])  # workspace left clean; deterministic
+    rel = ((outs[0] - outs[1]).norm() / outs[0].norm()).item()
+    assert rel < 2e-3, rel
+    # counters are back to zero
+    assert int(ws[:16384].view(torch.int32).abs().sum()) == 0
