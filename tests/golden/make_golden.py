@@ -138,6 +138,41 @@ def case_config1(ref, out: Path):
         counts=counts.astype(np.int16), density=float((z > 0).float().mean()))
 
 
+PUBLIC_NAMES = [
+    "packed_width", "allocate_packed_output", "packed_to_dense", "matmul_sparse",
+    "matmul_sparse_out", "matmul_t2d", "matmul_t2d_out", "matmul_gated_t2d",
+    "matmul_gated_t2d_out", "create_d2t_layer", "run_d2t_layer", "ensure_d2t_layer_shape",
+    "run_mlp_layer", "run_gated_mlp_layer", "_run_mlp_layer_with_hidden_states",
+    "_run_gated_mlp_layer_with_hidden_states", "run_mlp_layer_inplace",
+    "run_gated_mlp_layer_inplace", "_run_mlp_layer_inplace_with_hidden_states",
+    "_run_gated_mlp_layer_inplace_with_hidden_states", "destroy_d2t_layer",
+    "destroy_all_d2t_layers", "load_ext", "get_ext", "sparse_algorithms",
+    "D2TLayer", "D2TLinear", "T2DLinear", "GatedT2DLinear", "TwELLMLP", "TwELLGatedMLP",
+]
+
+
+def case_signatures(twell_ref, out: Path):
+    """Parameter names, order and defaults of the reference's public TwELL API."""
+    import inspect
+    import json
+    sigs = {}
+    for name in PUBLIC_NAMES:
+        obj = getattr(twell_ref, name)
+        target = obj.__init__ if inspect.isclass(obj) else obj
+        params = []
+        for p in inspect.signature(target).parameters.values():
+            if p.name == "self":
+                continue
+            default = None if p.default is inspect.Parameter.empty else repr(p.default)
+            params.append([p.name, p.kind.name, default])
+        sigs[name] = params
+        if inspect.isclass(obj):
+            sigs[name + ".methods"] = sorted(
+                m for m in vars(obj) if not m.startswith("__") and callable(getattr(obj, m)))
+    sigs["sparse_algorithms()"] = twell_ref.sparse_algorithms()
+    (out / "twell_signatures.json").write_text(json.dumps(sigs, indent=1, sort_keys=True))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -151,6 +186,7 @@ def main():
     twell_ref = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(twell_ref)
     torch.manual_seed(0)
+    case_signatures(twell_ref, HERE)
     case_small(ref, twell_ref, HERE)
     case_training(ref, HERE)
     case_config1(ref, HERE)
