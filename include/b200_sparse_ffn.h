@@ -110,6 +110,25 @@ int b200_twell_mlp(const void* x, const void* up, const void* down, void* packed
                    int num_splits, void* workspace, size_t workspace_bytes,
                    void* stream);
 
+/*
+ * Gated contraction for hosts that may not allocate device memory (no counterpart
+ * in the reference).  Same arguments and result as b200_twell_gated_t2d, minus the
+ * workspace: the scratch for the few-token shape is a 1 MiB array built into the
+ * library image (resident on every GPU that loads the library until exit), so the
+ * call makes no cudaMalloc / cudaFree and needs no caller buffer.
+ *   - Limit: M <= min(512, 129024 / D) tokens (63 at D = 2048, 31 at D = 4096);
+ *     larger M returns B200_EWORKSPACE - use b200_twell_gated_t2d there.
+ *   - The first call on each device resolves the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     before starting any stream capture.
+ *   - All calls on a device share the one array; the arrival counters in it are
+ *     cleared at every call.  Calls that can overlap on the GPU (two streams, two
+ *     host threads) race on it: issue them on one stream, or serialise them.
+ */
+int b200_twell_gated_t2d_noalloc(const void* x, const void* packed, const void* up,
+                                 const void* down, void* out, int64_t M, int64_t D,
+                                 int64_t H, int cf, uint32_t flags, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,6 +40,9 @@ _PROTOTYPES = {
                                      c_void_p]),
     "b200_twell_t2d": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_twell_gated_t2d_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_int64, c_int64, c_int64, c_int, c_uint32,
+                                             c_void_p]),
     "b200_twell_gated_mlp": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_int64, c_int64, c_int64, c_int, c_uint32,
                                      c_void_p, c_size_t, c_void_p]),

@@ -373,4 +373,95 @@ int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, con
                                    counters, stream);
 }
 
+int sm_count();  // c_api.cu
+
 }  // namespace b200
+
+// ---------------------------------------------------------------------------
+// Gated contraction for callers that must not allocate device memory.
+//
+// Some hosts hand a plugin a fixed set of buffers and forbid it to touch the
+// allocator: an inference server that planned all of its device memory up front,
+// a process whose pool belongs to another framework, a latency-critical loop in
+// which cudaMalloc's implicit device synchronisation is not acceptable.  Such a
+// caller still wants the few-token shape of the contraction (one token spread
+// over many clusters), which needs scratch memory for partial sums and arrival
+// counters.  Here that scratch is a fixed array inside the library image:
+// every GPU that loads the library holds these bytes until the process exits.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = (size_t)1 << 20;  // counters + fp32 partial sums
+
+// Device-side storage.  In host code this name is only a handle for
+// cudaGetSymbolAddress; it is never passed to a kernel directly.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch per device ordinal, resolved on first use.
+void* g_static_scratch_ptr[64] = {nullptr};
+
+int static_scratch_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess)
+    return b200::fail(B200_ECUDA, "b200_twell_gated_t2d_noalloc: cudaGetDevice: %s",
+                      cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64)
+    return b200::fail(B200_EUNSUPPORTED,
+                      "b200_twell_gated_t2d_noalloc: device ordinal %d is outside 0..63", dev);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);  // address on the CURRENT device
+    if (e != cudaSuccess || p == nullptr)
+      return b200::fail(B200_ECUDA, "b200_twell_gated_t2d_noalloc: cudaGetSymbolAddress: %s",
+                        cudaGetErrorString(e));
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return B200_OK;
+}
+
+// Largest token count the built-in scratch serves: two clusters per token must fit
+// their fp32 partial sums, and every token needs 8 arrival counters.
+int noalloc_max_tokens(int64_t D) {
+  const int64_t cap_floats = (int64_t)((kStaticScratchBytes - b200::kCounterWords * 4) / 4);
+  const int64_t by_partials = cap_floats / (2 * D);
+  const int64_t by_counters = (int64_t)b200::kCounterWords / 8;
+  return (int)(by_partials < by_counters ? by_partials : by_counters);
+}
+
+}  // namespace
+
+extern "C" int b200_twell_gated_t2d_noalloc(const void* x, const void* packed, const void* up,
+                                            const void* down, void* out, int64_t M, int64_t D,
+                                            int64_t H, int cf, uint32_t flags, void* stream) {
+  const char* fn = "b200_twell_gated_t2d_noalloc";
+  if (int rc = b200::check_dims(fn, M, D, H, cf)) return rc;
+  if (flags & ~B200_FLAG_HIGH_PRECISION)
+    return b200::fail(B200_EINVAL, "%s: unknown flags 0x%x", fn, flags);
+  const int max_tokens = noalloc_max_tokens(D);
+  if (M > max_tokens)
+    return b200::fail(B200_EWORKSPACE,
+                      "%s: M = %lld exceeds the built-in scratch (%zu bytes hold at most %d tokens "
+                      "at D = %lld); use b200_twell_gated_t2d with a caller workspace",
+                      fn, (long long)M, kStaticScratchBytes, max_tokens, (long long)D);
+  if (M == 0) return B200_OK;
+  const void* ptrs[5] = {x, packed, up, down, out};
+  const char* names[5] = {"x", "packed", "up", "down", "out"};
+  for (int i = 0; i < 5; ++i) {
+    if (ptrs[i] == nullptr) return b200::fail(B200_ENULL, "%s: %s is NULL", fn, names[i]);
+    if (!b200::aligned16(ptrs[i]))
+      return b200::fail(B200_EALIGN, "%s: %s is not 16-byte aligned", fn, names[i]);
+  }
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left behind: the arrival counters
+  // must start at zero (the partial sums are fully overwritten before they are read).
+  cudaError_t e = cudaMemsetAsync(scratch, 0, b200::kCounterWords * sizeof(unsigned int), st);
+  if (e != cudaSuccess)
+    return b200::fail(B200_ECUDA, "%s: cudaMemsetAsync: %s", fn, cudaGetErrorString(e));
+  return b200::twell_t2d_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, packed, up, down,
+                                out, M, D, H, cf, scratch, kStaticScratchBytes, b200::sm_count(),
+                                st);
+}
