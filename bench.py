@@ -238,7 +238,11 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    run_step = step if args.no_graph else capture(step, device).replay
+    # Multi-rank steps are launched eagerly: a step captured together with its NCCL
+    # all-reduces stalled on this software stack (2 ranks, no error raised), so graphs are
+    # used only where the step has no collective.
+    graphed = not args.no_graph and not dist_on
+    run_step = capture(step, device).replay if graphed else step
     ms_step = time_replays(run_step, args.steps, args.warmup, device, dist_on)
     clocks = sampler.stop() if rank == 0 else None
 
@@ -283,6 +287,7 @@ def run_ours(args):
                    "layers": L, "d_model": d, "d_ff": args.d_ff, "batch": B,
                    "d_ff_shard": [h0, h1], "parallelism": f"dff_shard{world}",
                    "l2": "weights (2.8 GB) exceed L2; no flush needed",
+                   "cuda_graph": graphed,
                    "nnz_per_token_last_layer": nnz_per_token,
                    "active_union_last_layer": union,
                    "ms_per_layer": ms_step / L,
@@ -290,7 +295,10 @@ def run_ours(args):
                    "ffn_algorithmic_gbs": ffn_bytes / (ms_step / L * 1e-3) / 1e9},
         "roofline": {"bound": "hbm", "kernel": "twell_pack_kernel", "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None,
+                     "frac": achieved / peak,
+                     # ncu dram__bytes_read+write per launch = 1.00 x the algorithmic bytes
+                     # (profiles/decode_ffn_batch32_pack_and_contraction.md), scaled to this launch
+                     "traffic": float(pack_bytes),
                      "us_per_launch": ms_pack * 1e3, "algorithmic_bytes": pack_bytes},
         "gpu_launches": args.steps * L * 2,
         "clocks": clocks,
@@ -421,6 +429,10 @@ def run_reference(args):
 
 def main():
     args = parse()
+    watchdog = int(os.environ.get("B200_BENCH_WATCHDOG_S", "0"))
+    if watchdog > 0:  # dump every thread's stack and exit instead of hanging silently
+        import faulthandler
+        faulthandler.dump_traceback_later(watchdog, exit=True)
     if args.impl == "reference":
         run_reference(args)
         return

@@ -1,0 +1,96 @@
+"""d_ff-sharded sparse gated FFN: one process per GPU, one all-reduce on the output.
+
+In the TwELL layout all three weights are ``[H, D]`` (reference:
+custom_models/sparse_testing_utils.py:26-28), so a d_ff shard is the same
+contiguous row range ``[h0, h1)`` of GATE, UP and DOWN.  Shard boundaries are
+multiples of 256 neurons (one TwELL tile); shards may be uneven (11008 = 43 tiles).
+Every rank packs and contracts its own shard with *local* column indices and
+produces a partial ``y_r [M, D]``; the partials are summed with a single
+all-reduce.  The reference has no tensor parallelism (data parallel only), so
+this module has no counterpart there.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+TILE = 256
+
+
+def shard_range(d_ff: int, rank: int, world_size: int) -> tuple[int, int]:
+    """Row range ``[h0, h1)`` of ``rank``: tile-granular, contiguous, sizes differ by at most
+    one tile, earlier ranks take the larger shards."""
+    if d_ff % TILE:
+        raise ValueError(f"d_ff must be a multiple of {TILE}")
+    if not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} outside 0..{world_size - 1}")
+    tiles = d_ff // TILE
+    if tiles < world_size:
+        raise ValueError(f"d_ff={d_ff} has {tiles} tiles, fewer than world_size={world_size}")
+    base, rem = divmod(tiles, world_size)
+    start = rank * base + min(rank, rem)
+    n = base + (1 if rank < rem else 0)
+    return start * TILE, (start + n) * TILE
+
+
+def shard_weights(GATE: torch.Tensor, UP: torch.Tensor, DOWN: torch.Tensor, rank: int,
+                  world_size: int):
+    """This rank's contiguous copies of the three ``[H, D]`` weights."""
+    h = UP.shape[0]
+    if DOWN.shape[0] != h or (GATE is not None and GATE.shape[0] != h):
+        raise ValueError("GATE / UP / DOWN must all be [H, D] (DOWN = down_proj.weight.T)")
+    h0, h1 = shard_range(h, rank, world_size)
+    g = None if GATE is None else GATE[h0:h1].contiguous()
+    return g, UP[h0:h1].contiguous(), DOWN[h0:h1].contiguous()
+
+
+class ShardedTwELLGatedMLP(nn.Module):
+    """``TwELLGatedMLP`` over a d_ff shard plus the all-reduce of the FFN output.
+
+    ``GATE/UP/DOWN`` are the FULL ``[H, D]`` weights unless ``presharded=True``.
+    ``local_factory(layer_number, GATE, UP, DOWN, **kwargs)`` builds the per-rank module; it
+    defaults to :class:`sparser_faster_llms_b200.twell.TwELLGatedMLP` (CUDA only).
+    """
+
+    def __init__(self, layer_number: int, GATE: torch.Tensor, UP: torch.Tensor,
+                 DOWN: torch.Tensor, *, process_group=None, rank: int | None = None,
+                 world_size: int | None = None, presharded: bool = False,
+                 reduce_dtype: torch.dtype | None = None,
+                 local_factory: Callable[..., nn.Module] | None = None, **twell_kwargs):
+        super().__init__()
+        self.process_group = process_group
+        if world_size is None:
+            world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        if rank is None:
+            rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        self.rank, self.world_size = int(rank), int(world_size)
+        self.d_ff = int(UP.shape[0]) if not presharded else None
+        if presharded:
+            g, u, d = GATE.contiguous(), UP.contiguous(), DOWN.contiguous()
+            self.h_range = None
+        else:
+            g, u, d = shard_weights(GATE, UP, DOWN, self.rank, self.world_size)
+            self.h_range = shard_range(UP.shape[0], self.rank, self.world_size)
+        if local_factory is None:
+            from .twell import TwELLGatedMLP
+            local_factory = TwELLGatedMLP
+        self.local = local_factory(layer_number, g, u, d, **twell_kwargs)
+        self.reduce_dtype = reduce_dtype
+
+    def forward(self, A: torch.Tensor) -> torch.Tensor:
+        y = self.local(A)
+        if self.world_size > 1:
+            if self.reduce_dtype is not None and self.reduce_dtype != y.dtype:
+                acc = y.to(self.reduce_dtype)
+                dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=self.process_group)
+                y = acc.to(y.dtype)
+            else:
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.process_group)
+        return y
+
+    def destroy(self) -> None:
+        if hasattr(self.local, "destroy"):
+            self.local.destroy()
