@@ -110,6 +110,79 @@ int b200_twell_mlp(const void* x, const void* up, const void* down, void* packed
                    int num_splits, void* workspace, size_t workspace_bytes,
                    void* stream);
 
+/* ------------------------------------------------------------------------
+ * Hybrid sparse training operator (custom_models/hybrid_modules).
+ * Every sparse operand is a slab-shaped uint32 array with the layout of `packed`:
+ * word (row, tile, slot) = col | bf16(value) << 16 for the same entry as the
+ * pattern P produced by b200_twell_pack; count words are copied from P.
+ * ------------------------------------------------------------------------ */
+
+/*
+ * Forward: R = (x k_w^T) sampled at P's pattern (bf16), T = R * P (bf16 multiply),
+ * row_l1[r] = sum |T[r,:]| (fp32), row_nnz[r] = true positive count of the row,
+ * row_drop[r] = entries of the row lost to slab overflow.  Replaces
+ * new_product_as_sparse_sma + sparse_elementwise of ff_forward_cuda_gated
+ * (custom_models/hybrid_modules/custom_op.cpp:131-132; kernels hybrid_sp.cu:711-805,
+ * :1480-1587).
+ */
+int b200_hybrid_sddmm_fwd(const void* x, const void* k_w, const void* p_slab, void* r_slab,
+                          void* t_slab, float* row_l1, int* row_nnz, int* row_drop,
+                          int64_t M, int64_t D, int64_t H, int cf, void* stream);
+
+/*
+ * Backward: dT = (g_out v_w^T) at the pattern (bf16) + (*l1_grad / M) * sign(R) (bf16),
+ * dR = dT * P, dU = dT * R.  Replaces the dT / L1-shift / dR / dU steps of
+ * ff_backward_cuda_gated (custom_op.cpp:203-222; hybrid_sp.cu:711-805, :1754-1779,
+ * :1480-1664).  l1_grad: device pointer to the fp32 gradient of l1 (NULL = 0); it is
+ * read on the device, so the host never waits for it.
+ */
+int b200_hybrid_sddmm_bwd(const void* g_out, const void* v_w, const void* p_slab,
+                          const void* r_slab, void* dr_slab, void* du_slab,
+                          const float* l1_grad, int64_t M, int64_t D, int64_t H, int cf,
+                          void* stream);
+
+/*
+ * Row product: out[r,:] = sum over row r's entries of value * b_rows[col,:], fp32 fma,
+ * bf16 store.  Replaces sparse_dense_gemm_hybrid_dense (custom_op.cpp:133, :239-245;
+ * hybrid_sp.cu:222-301, :1320-1396).  Workspace as for b200_twell_gated_t2d.
+ */
+int b200_hybrid_spmm(const void* vals_slab, const void* b_rows, void* out, int64_t M,
+                     int64_t D, int64_t H, int cf, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
+/*
+ * Column lists of the pattern: col_start[H+1] (exclusive scan of per-column counts) and,
+ * for list position i, csc_row[i] = row and csc_pos[i] = word index into a slab array.
+ * col_count[H], cursor[H], overflow[1] are scratch / status (overflow = entries beyond
+ * `capacity`).  Order inside a column follows atomic arrival (as the reference's scatter
+ * transpose does).  Replaces transpose_hybrid_dense (custom_op.cpp:182-237;
+ * hybrid_sp.cu:1042-1214).
+ */
+int b200_hybrid_csc_build(const void* p_slab, int* col_count, int* col_start, int* cursor,
+                          int* csc_row, int* csc_pos, int64_t capacity, int* overflow,
+                          int64_t M, int64_t H, int cf, void* stream);
+
+/*
+ * Transposed product(s): out0[j,:] = sum over column j's list of value(vals0) * b_rows[row,:]
+ * (and out1 from vals1 over the same rows when vals1 != NULL).  fp32 fma, bf16 store,
+ * out [H, D].  Replaces the three sparse_dense_gemm_hybrid_dense calls on transposed
+ * operands (custom_op.cpp:261-269).
+ */
+int b200_hybrid_spmm_t(const void* vals0, const void* vals1, const int* col_start,
+                       const int* csc_row, const int* csc_pos, int64_t capacity,
+                       const void* b_rows, void* out0, void* out1, int64_t H, int64_t D,
+                       void* stream);
+
+/*
+ * Row-ELL x dense: C[r,:] = sum_k vals[r,k] * B[cols[r,k],:] for rows with
+ * 0 < row_counts[r] <= overflow_threshold, zeros otherwise.  vals bf16 / cols uint16
+ * [M, ell_stride], B [K, N] bf16, C [M, N] bf16.  Replaces ell_spmm_raw
+ * (custom_op.cpp:313; hybrid_sp.cu:222-301).
+ */
+int b200_hybrid_ell_spmm_raw(const void* ell_vals, const void* ell_cols, const int* row_counts,
+                             const void* b, void* c, int64_t M, int64_t K, int64_t N,
+                             int64_t ell_stride, int64_t overflow_threshold, void* stream);
+
 /*
  * Gated contraction for hosts that may not allocate device memory (no counterpart
  * in the reference).  Same arguments and result as b200_twell_gated_t2d, minus the

@@ -7,7 +7,7 @@ current CUDA stream.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_int, c_int64, c_size_t, c_uint32, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
 import torch
@@ -40,6 +40,16 @@ _PROTOTYPES = {
                                      c_void_p]),
     "b200_twell_t2d": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_hybrid_sddmm_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "b200_hybrid_sddmm_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int64, c_int,
+                                                       c_void_p]),
+    "b200_hybrid_spmm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                 c_void_p, c_size_t, c_void_p]),
+    "b200_hybrid_csc_build": (c_int, [c_void_p] * 6 + [c_int64, c_void_p, c_int64, c_int64, c_int,
+                                                       c_void_p]),
+    "b200_hybrid_spmm_t": (c_int, [c_void_p] * 5 + [c_int64, c_void_p, c_void_p, c_void_p, c_int64,
+                                                    c_int64, c_void_p]),
+    "b200_hybrid_ell_spmm_raw": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_void_p]),
     "b200_twell_gated_t2d_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_int64, c_int64, c_int64, c_int, c_uint32,
                                              c_void_p]),

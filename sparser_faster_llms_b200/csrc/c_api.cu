@@ -119,6 +119,20 @@ int b200_twell_t2d(const void* packed, const void* down, void* out, int64_t M, i
                           static_cast<cudaStream_t>(stream));
 }
 
+int b200_hybrid_spmm(const void* vals_slab, const void* b_rows, void* out, int64_t M, int64_t D,
+                     int64_t H, int cf, void* workspace, size_t workspace_bytes, void* stream) {
+  const char* fn = "b200_hybrid_spmm";
+  B200_TRY(check_dims(fn, M, D, H, cf));
+  if (M == 0) return B200_OK;
+  B200_TRY(check_ptr(fn, "vals_slab", vals_slab));
+  B200_TRY(check_ptr(fn, "b_rows", b_rows));
+  B200_TRY(check_ptr(fn, "out", out));
+  B200_TRY(check_workspace(fn, workspace));
+  return twell_t2d_launch(false, true, nullptr, vals_slab, nullptr, b_rows, out, M, D, H, cf,
+                          workspace, workspace_bytes, sm_count(),
+                          static_cast<cudaStream_t>(stream));
+}
+
 int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias, const void* up,
                          const void* down, void* packed, void* out, int64_t M, int64_t D,
                          int64_t H, int cf, uint32_t flags, void* workspace,

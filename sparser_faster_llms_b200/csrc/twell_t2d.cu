@@ -369,8 +369,10 @@ int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, con
               : dispatch_ni<true, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
                                          counters, stream);
   }
-  return dispatch_ni<false, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                   counters, stream);
+  return hp ? dispatch_ni<false, true>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
+                                       counters, stream)
+            : dispatch_ni<false, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
+                                        counters, stream);
 }
 
 int sm_count();  // c_api.cu

@@ -1,0 +1,373 @@
+"""Hybrid sparse training operator: ``torch.ops.sparse_ops.ff_forward_gated`` and friends.
+
+Python/torch host side of the reference's ``custom_models/hybrid_modules/custom_op.cpp``.
+The math is
+
+    P = relu(X G^T)           (pattern + values, TwELL slabs from the pack kernel)
+    R = (X K^T) on P's pattern,   T = R * P
+    out = T V,   l0 = mean_rows nnz(P),   l1 = mean_rows sum |T|
+
+and its backward (custom_op.cpp:139-282).  Every sparse operand is a slab-shaped
+``uint32`` tensor aligned with P (see ``csrc/hybrid_ops.cu``); the reference's
+row-ELL + dense-tail container ``hybrid_sp_t`` and its conversion / transpose
+kernels have no equivalent here because nothing is converted.
+
+Registered operators (same names and argument order as custom_op.cpp:308-342, :424-427):
+
+    sparse_ops::ff_forward_gated(X, G, K, V) -> (out, l0, l1, P, R, T)
+    sparse_ops::ff_backward_gated(X, G, K, V, P, R, T, gR, gl0, gl1) -> (dX, dG, dK, dV)
+    sparse_ops::ell_spmm_raw(ell_vals, ell_cols, row_counts, B, M, K, N, ell_stride, thr)
+    sparse_ops_config::set_ell_width_regular / set_ell_width_transpose /
+        set_tail_rows_regular / set_tail_rows_transpose / set_discard_overflow /
+        get_last_transpose_overflow_count
+    sparse_ops_perf::print_report / reset_stats
+
+P, R, T are returned as int32 tensors (a Python-registered operator cannot return a
+TorchScript custom class); :class:`HybridSp` wraps one of them for callers that want
+``overflow_count_tensor()``.  There is no CPU implementation.
+"""
+from __future__ import annotations
+
+import os
+import time
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+TILE = 256
+
+# ----------------------------------------------------------------------------
+# knobs (reference: hybrid_sp.cu:634-646, KNOBS.md)
+# ----------------------------------------------------------------------------
+_CONFIG = {
+    # entries kept per 256-column tile of a row: 31 / 63 / 127 (slab width 32 / 64 / 128 words).
+    # The reference's "ELL width" (entries per row, default 128) maps onto the slab width.
+    "ell_width_regular": 128,
+    "ell_width_transpose": 256,
+    "tail_rows_regular": 2048,
+    "tail_rows_transpose": 2048,
+    "discard_overflow": 0,
+    # average stored entries per row the column lists are sized for
+    "csc_entries_per_row": 512,
+}
+_LAST_TRANSPOSE_OVERFLOW: torch.Tensor | None = None
+_PERF: dict[str, list[float]] = {}
+_PERF_ENABLED = os.environ.get("SPARSE_ENABLE_PERF_PROFILING", "0") not in ("0", "", "false", "False")
+
+
+def compression_factor() -> int:
+    """Slab compression factor implied by ``ell_width_regular``: the per-tile capacity is
+    the smallest of 31 / 63 / 127 that is >= ell_width / 4 (a row of 4096 neurons has 16
+    tiles, so the default 128 entries per row never overflows a 63-entry tile on average)."""
+    per_tile = max(1, _CONFIG["ell_width_regular"] // 4)
+    if per_tile <= 31:
+        return 8
+    if per_tile <= 63:
+        return 4
+    return 2
+
+
+@dataclass
+class HybridSp:
+    """Slab-shaped sparse operand (pattern P, or values aligned with P)."""
+    slab: torch.Tensor          # int32 [M, tiles * W]
+    m: int
+    n: int
+    cf: int
+    dropped: torch.Tensor | None = None  # int32 scalar: entries lost to slab overflow
+
+    def overflow_count_tensor(self) -> torch.Tensor:
+        if self.dropped is None:
+            return torch.zeros((), dtype=torch.int32, device=self.slab.device)
+        return self.dropped
+
+
+class _Timer:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if _PERF_ENABLED:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e1 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _PERF_ENABLED:
+            self.e1.record()
+            self.e1.synchronize()
+            _PERF.setdefault(self.name, []).append(self.e0.elapsed_time(self.e1))
+        return False
+
+
+def _check_inputs(X, G, K, V):
+    for name, t in (("X", X), ("G", G), ("K", K), ("V", V)):
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor: sparse_ops has no CPU implementation")
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError(f"{name}: Expected a bfloat16 tensor but got {t.dtype}")
+    if X.dim() != 3:
+        raise ValueError(f"X must be [B, S, D], got {tuple(X.shape)}")
+    h, d = K.shape
+    if G.shape != (h, d) or V.shape != (h, d) or X.shape[-1] != d:
+        raise ValueError(
+            f"G, K, V must all be [H, D] with D = X.shape[-1]; got {tuple(G.shape)}, "
+            f"{tuple(K.shape)}, {tuple(V.shape)}, X {tuple(X.shape)}")
+    return h, d
+
+
+def _slab_shape(m: int, h: int, cf: int) -> tuple[int, int]:
+    if h % TILE:
+        raise ValueError(f"H must be a multiple of {TILE}")
+    return m, (h // TILE) * (TILE // cf)
+
+
+def _spmm(vals: torch.Tensor, B: torch.Tensor, m: int, d: int, h: int, cf: int) -> torch.Tensor:
+    """Row product ``out[r,:] = sum value * B[col,:]`` (fp32 fma, bf16 store)."""
+    out = torch.empty((m, d), dtype=torch.bfloat16, device=vals.device)
+    _lib.call("b200_hybrid_spmm", vals.device, vals.data_ptr(), B.data_ptr(), out.data_ptr(),
+              m, d, h, cf, *_lib.workspace(vals.device))
+    return out
+
+
+def ff_forward_impl(X: torch.Tensor, G: torch.Tensor, K: torch.Tensor, V: torch.Tensor):
+    """Forward of the hybrid operator (custom_op.cpp:40-137).  Returns
+    ``(out [B,S,D] bf16, l0 [], l1 [], P, R, T, dropped)`` with P/R/T int32 slab tensors."""
+    h, d = _check_inputs(X, G, K, V)
+    m = X.shape[0] * X.shape[1]
+    cf = compression_factor()
+    dev = X.device
+    Xf = X.reshape(m, d).contiguous()
+    G, K, V = G.contiguous(), K.contiguous(), V.contiguous()
+    shape = _slab_shape(m, h, cf)
+    with _Timer("ff_forward_gated_total"):
+        P = torch.empty(shape, dtype=torch.int32, device=dev)
+        with _Timer("gate_gemm_pack"):
+            _lib.call("b200_twell_pack", dev, Xf.data_ptr(), G.data_ptr(), None, P.data_ptr(),
+                      m, d, h, cf)
+        R = torch.empty_like(P)
+        T = torch.empty_like(P)
+        row_l1 = torch.empty(m, dtype=torch.float32, device=dev)
+        row_nnz = torch.empty(m, dtype=torch.int32, device=dev)
+        row_drop = torch.empty(m, dtype=torch.int32, device=dev)
+        with _Timer("sddmm_R_T"):
+            _lib.call("b200_hybrid_sddmm_fwd", dev, Xf.data_ptr(), K.data_ptr(), P.data_ptr(),
+                      R.data_ptr(), T.data_ptr(), row_l1.data_ptr(), row_nnz.data_ptr(),
+                      row_drop.data_ptr(), m, d, h, cf)
+        with _Timer("spmm_out"):
+            out = _spmm(T, V, m, d, h, cf)
+        inv_m = 1.0 / max(m, 1)
+        l0 = row_nnz.sum(dtype=torch.float32) * inv_m
+        l1 = row_l1.sum() * inv_m
+        dropped = row_drop.sum(dtype=torch.int32)
+    return out.reshape(X.shape), l0, l1, P, R, T, dropped
+
+
+_CSC_SCRATCH: dict[tuple, dict[str, torch.Tensor]] = {}
+
+
+def _csc_scratch(dev: torch.device, m: int, h: int) -> dict[str, torch.Tensor]:
+    cap = int(min(m * _CONFIG["csc_entries_per_row"], 2**31 - 1))
+    key = (dev.index, m, h, cap)
+    buf = _CSC_SCRATCH.get(key)
+    if buf is None:
+        _CSC_SCRATCH.clear()  # one shape at a time: the lists are rebuilt by every backward
+        i32 = dict(dtype=torch.int32, device=dev)
+        buf = {"count": torch.empty(h, **i32), "start": torch.empty(h + 1, **i32),
+               "cursor": torch.empty(h, **i32), "row": torch.empty(max(cap, 1), **i32),
+               "pos": torch.empty(max(cap, 1), **i32), "cap": cap}
+        _CSC_SCRATCH[key] = buf
+    return buf
+
+
+def ff_backward_impl(X, G, K, V, P, R, T, gR, gl0, gl1):
+    """Backward of the hybrid operator (custom_op.cpp:139-282).  ``gl0`` is ignored, as in
+    the reference.  Returns ``(dX [B,S,D], dG, dK, dV [H,D])`` in bf16."""
+    global _LAST_TRANSPOSE_OVERFLOW
+    h, d = _check_inputs(X, G, K, V)
+    m = X.shape[0] * X.shape[1]
+    cf = compression_factor()
+    dev = X.device
+    if tuple(P.shape) != _slab_shape(m, h, cf):
+        raise ValueError("P does not match the current slab width: the ELL-width knob changed "
+                         "between forward and backward")
+    if gR.dtype != torch.bfloat16:
+        raise RuntimeError(f"gR: Expected a bfloat16 tensor but got {gR.dtype}")
+    Xf = X.reshape(m, d).contiguous()
+    gRf = gR.reshape(m, d).contiguous()
+    G, K, V = G.contiguous(), K.contiguous(), V.contiguous()
+    gl1_dev = None
+    if gl1 is not None:
+        gl1_dev = gl1.detach().to(device=dev, dtype=torch.float32).reshape(1).contiguous()
+    with _Timer("ff_backward_gated_total"):
+        dR = torch.empty_like(P)
+        dU = torch.empty_like(P)
+        with _Timer("sddmm_dT_dR_dU"):
+            _lib.call("b200_hybrid_sddmm_bwd", dev, gRf.data_ptr(), V.data_ptr(), P.data_ptr(),
+                      R.data_ptr(), dR.data_ptr(), dU.data_ptr(), _lib.ptr(gl1_dev), m, d, h, cf)
+        with _Timer("spmm_dX"):
+            dX = _spmm(dR, K, m, d, h, cf) + _spmm(dU, G, m, d, h, cf)
+        sc = _csc_scratch(dev, m, h)
+        overflow = torch.empty(1, dtype=torch.int32, device=dev)
+        with _Timer("column_lists"):
+            _lib.call("b200_hybrid_csc_build", dev, P.data_ptr(), sc["count"].data_ptr(),
+                      sc["start"].data_ptr(), sc["cursor"].data_ptr(), sc["row"].data_ptr(),
+                      sc["pos"].data_ptr(), sc["cap"], overflow.data_ptr(), m, h, cf)
+        dK = torch.empty((h, d), dtype=torch.bfloat16, device=dev)
+        dG = torch.empty_like(dK)
+        dV = torch.empty_like(dK)
+        with _Timer("spmm_t_dK_dG"):
+            _lib.call("b200_hybrid_spmm_t", dev, dR.data_ptr(), dU.data_ptr(),
+                      sc["start"].data_ptr(), sc["row"].data_ptr(), sc["pos"].data_ptr(),
+                      sc["cap"], Xf.data_ptr(), dK.data_ptr(), dG.data_ptr(), h, d)
+        with _Timer("spmm_t_dV"):
+            _lib.call("b200_hybrid_spmm_t", dev, T.data_ptr(), None, sc["start"].data_ptr(),
+                      sc["row"].data_ptr(), sc["pos"].data_ptr(), sc["cap"], gRf.data_ptr(),
+                      dV.data_ptr(), None, h, d)
+        _LAST_TRANSPOSE_OVERFLOW = overflow.reshape(())
+    return dX.reshape(X.shape), dG, dK, dV
+
+
+def ell_spmm_raw_impl(ell_vals, ell_cols, row_counts, B, M, K, N, ell_stride,
+                      overflow_threshold):
+    """Row-ELL x dense (custom_op.cpp:313): bf16 values, 16-bit columns, int32 counts."""
+    if ell_vals.dtype != torch.bfloat16 or B.dtype != torch.bfloat16:
+        raise RuntimeError("ell_spmm_raw: ell_vals and B must be bfloat16")
+    if ell_cols.dtype not in (torch.int16, torch.uint16):
+        raise RuntimeError("ell_spmm_raw: ell_cols must be a 16-bit integer tensor")
+    if row_counts.dtype != torch.int32:
+        raise RuntimeError("ell_spmm_raw: row_counts must be int32")
+    dev = B.device
+    C = torch.empty((int(M), int(N)), dtype=torch.bfloat16, device=dev)
+    _lib.call("b200_hybrid_ell_spmm_raw", dev, ell_vals.contiguous().data_ptr(),
+              ell_cols.contiguous().data_ptr(), row_counts.contiguous().data_ptr(),
+              B.contiguous().data_ptr(), C.data_ptr(), int(M), int(K), int(N), int(ell_stride),
+              int(overflow_threshold))
+    return C
+
+
+# ----------------------------------------------------------------------------
+# operator registration
+# ----------------------------------------------------------------------------
+_REGISTERED = False
+_LIBS: list = []  # keeps the torch.library.Library objects alive
+
+_FWD = "sparse_ops::ff_forward_gated"
+_BWD = "sparse_ops::ff_backward_gated"
+
+
+def _fake_forward(X, G, K, V):
+    m = X.shape[0] * X.shape[1]
+    shape = _slab_shape(m, K.shape[0], compression_factor())
+    slab = lambda: torch.empty(shape, dtype=torch.int32, device=X.device)  # noqa: E731
+    scalar = lambda: torch.empty((), dtype=torch.float32, device=X.device)  # noqa: E731
+    return (torch.empty(X.shape, dtype=torch.bfloat16, device=X.device), scalar(), scalar(),
+            slab(), slab(), slab())
+
+
+def _fake_backward(X, G, K, V, P, R, T, gR, gl0, gl1):
+    e = lambda t: torch.empty(t.shape, dtype=torch.bfloat16, device=t.device)  # noqa: E731
+    return e(X), e(G), e(K), e(V)
+
+
+def _setup_context(ctx, inputs, output):
+    X, G, K, V = inputs
+    _, _, _, P, R, T = output
+    ctx.save_for_backward(X, G, K, V, P, R, T)
+    ctx.set_materialize_grads(False)
+
+
+def _autograd_backward(ctx, g_out, g_l0, g_l1, g_p, g_r, g_t):
+    X, G, K, V, P, R, T = ctx.saved_tensors
+    if g_out is None:
+        g_out = torch.zeros_like(X)
+    zero = torch.zeros((), dtype=torch.float32, device=X.device)
+    dX, dG, dK, dV = torch.ops.sparse_ops.ff_backward_gated(
+        X, G, K, V, P, R, T, g_out.to(torch.bfloat16), zero if g_l0 is None else g_l0,
+        zero if g_l1 is None else g_l1)
+    return dX, dG, dK, dV
+
+
+def register_ops() -> None:
+    """Define and implement the operators (idempotent)."""
+    global _REGISTERED
+    if _REGISTERED:
+        return
+    lib = torch.library.Library("sparse_ops", "DEF")
+    lib.define("ff_forward_gated(Tensor X, Tensor G, Tensor K, Tensor V) -> "
+               "(Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
+    lib.define("ff_backward_gated(Tensor X, Tensor G, Tensor K, Tensor V, Tensor P, Tensor R, "
+               "Tensor T, Tensor gR, Tensor gl0, Tensor gl1) -> (Tensor, Tensor, Tensor, Tensor)")
+    lib.define("ell_spmm_raw(Tensor ell_vals, Tensor ell_cols, Tensor row_counts, Tensor B, int M, "
+               "int K, int N, int ell_stride, int overflow_threshold) -> Tensor")
+    lib.impl("ff_forward_gated", lambda X, G, K, V: ff_forward_impl(X, G, K, V)[:6], "CUDA")
+    lib.impl("ff_backward_gated", ff_backward_impl, "CUDA")
+    lib.impl("ell_spmm_raw", ell_spmm_raw_impl, "CUDA")
+    torch.library.register_fake(_FWD, _fake_forward, lib=lib)
+    torch.library.register_fake(_BWD, _fake_backward, lib=lib)
+    torch.library.register_autograd(_FWD, _autograd_backward, setup_context=_setup_context,
+                                    lib=lib)
+    torch.library.register_autocast(_FWD, "cuda", torch.bfloat16, lib=lib)
+    _LIBS.append(lib)
+
+    cfg = torch.library.Library("sparse_ops_config", "DEF")
+    for name in ("set_ell_width_regular", "set_ell_width_transpose", "set_tail_rows_regular",
+                 "set_tail_rows_transpose", "set_discard_overflow"):
+        cfg.define(f"{name}(int v) -> ()")
+        cfg.impl(name, (lambda key: lambda v: _set_knob(key, v))(name[4:]),
+                 "CompositeExplicitAutograd")
+    cfg.define("get_last_transpose_overflow_count() -> Tensor")
+    cfg.impl("get_last_transpose_overflow_count", _get_last_transpose_overflow,
+             "CompositeExplicitAutograd")
+    _LIBS.append(cfg)
+
+    perf = torch.library.Library("sparse_ops_perf", "DEF")
+    perf.define("print_report() -> ()")
+    perf.define("reset_stats() -> ()")
+    perf.impl("print_report", print_report, "CompositeExplicitAutograd")
+    perf.impl("reset_stats", reset_stats, "CompositeExplicitAutograd")
+    _LIBS.append(perf)
+    _REGISTERED = True
+
+
+def _set_knob(key: str, v: int) -> None:
+    v = int(v)
+    if v < 0:
+        raise ValueError(f"{key} must be >= 0")
+    _CONFIG[key] = v
+
+
+def _get_last_transpose_overflow() -> torch.Tensor:
+    if _LAST_TRANSPOSE_OVERFLOW is None:
+        raise RuntimeError("No backward pass has been run yet")
+    return _LAST_TRANSPOSE_OVERFLOW
+
+
+def print_report() -> None:
+    """Per-section CUDA-event timings (enabled by SPARSE_ENABLE_PERF_PROFILING=1);
+    reference: perf_instrumentation.h:86-216."""
+    if not _PERF:
+        print("[sparse_ops_perf] no samples (set SPARSE_ENABLE_PERF_PROFILING=1)")
+        return
+    print(f"[sparse_ops_perf] {time.strftime('%H:%M:%S')}")
+    for name, xs in sorted(_PERF.items()):
+        s = sorted(xs)
+        mean = sum(xs) / len(xs)
+        print(f"  {name:28s} n={len(xs):5d} mean={mean:8.3f} ms min={s[0]:8.3f} "
+              f"p50={s[len(s) // 2]:8.3f} max={s[-1]:8.3f}")
+
+
+def reset_stats() -> None:
+    _PERF.clear()
+
+
+def ff_forward_gated(X, G, K, V):
+    """Direct (non-dispatcher) forward returning :class:`HybridSp` objects like the
+    reference's CUDA implementation (custom_op.cpp:40-137)."""
+    out, l0, l1, P, R, T, dropped = ff_forward_impl(X, G, K, V)
+    m, h, cf = X.shape[0] * X.shape[1], K.shape[0], compression_factor()
+    wrap = lambda t: HybridSp(t, m, h, cf, dropped)  # noqa: E731
+    return out, l0, l1, wrap(P), wrap(R), wrap(T)
