@@ -68,6 +68,24 @@ int b200_twell_pack(const void* x, const void* w, const float* bias, void* packe
                     int64_t M, int64_t D, int64_t H, int cf, void* stream);
 
 /*
+ * Same as b200_twell_pack with the kernel family chosen by the caller:
+ *   kernel 0 = automatic (M <= 32: split-k cluster kernel on mma.sync, HBM-bound;
+ *              M > 32: tcgen05 / TMEM / TMA kernel),
+ *   kernel 1 = split-k cluster kernel, kernel 2 = tcgen05 kernel.
+ * Both produce identical slab bytes on exact-arithmetic inputs.  No reference
+ * counterpart (the reference has one WGMMA kernel, matmul_d2t.cu:287-709).
+ */
+int b200_twell_pack_select(const void* x, const void* w, const float* bias, void* packed,
+                           int64_t M, int64_t D, int64_t H, int cf, int kernel, void* stream);
+
+/*
+ * Error word of the tcgen05 kernel: 0, or the role (1 producer, 2 mma, 3 epilogue) whose
+ * bounded mbarrier wait gave up; -1 if it cannot be read.  Reads and clears the word;
+ * synchronises the device (a diagnostic, not part of the hot path).
+ */
+int b200_twell_pack_tc_status(void);
+
+/*
  * Gated TwELL -> dense contraction:
  *   out[r,:] = sum over stored (j, g) of row r:  (g * (x[r,:] . up[j,:])) * down[j,:]
  * Replaces matmul_gated_t2d_out and its flex / high-precision / in-place

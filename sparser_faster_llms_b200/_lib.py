@@ -35,6 +35,9 @@ _PROTOTYPES = {
     "b200_workspace_bytes": (c_size_t, []),
     "b200_twell_pack": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                 c_int64, c_int, c_void_p]),
+    "b200_twell_pack_select": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                       c_int64, c_int, c_int, c_void_p]),
+    "b200_twell_pack_tc_status": (c_int, []),
     "b200_twell_gated_t2d": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                      c_int64, c_int64, c_int, c_uint32, c_void_p, c_size_t,
                                      c_void_p]),

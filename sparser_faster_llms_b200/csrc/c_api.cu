@@ -20,6 +20,9 @@ int fail(int code, const char* fmt, ...) {
 
 int twell_pack_small(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                      int64_t D, int64_t H, int cf, cudaStream_t stream);
+int twell_pack_tc(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                  int64_t D, int64_t H, int cf, cudaStream_t stream);
+int twell_pack_tc_status();
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
                      void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
@@ -71,18 +74,32 @@ const char* b200_last_error(void) { return last_error_buffer(); }
 
 size_t b200_workspace_bytes(void) { return (size_t)1 << 20; }
 
-int b200_twell_pack(const void* x, const void* w, const float* bias, void* packed, int64_t M,
-                    int64_t D, int64_t H, int cf, void* stream) {
+int b200_twell_pack_select(const void* x, const void* w, const float* bias, void* packed,
+                           int64_t M, int64_t D, int64_t H, int cf, int kernel, void* stream) {
   const char* fn = "b200_twell_pack";
   B200_TRY(check_dims(fn, M, D, H, cf));
+  if (kernel < 0 || kernel > 2) return fail(B200_EINVAL, "%s: kernel must be 0, 1 or 2", fn);
   if (M == 0) return B200_OK;
   B200_TRY(check_ptr(fn, "x", x));
   B200_TRY(check_ptr(fn, "w", w));
   B200_TRY(check_ptr(fn, "packed", packed));
   if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 3u))
     return fail(B200_EALIGN, "%s: bias is not 4-byte aligned", fn);
-  return twell_pack_small(x, w, bias, packed, M, D, H, cf, static_cast<cudaStream_t>(stream));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Up to one 32-token tile the weight stream is read once and the split-k mma.sync
+  // kernel is HBM-bound; beyond that the tcgen05 kernel reuses each weight tile for up
+  // to 128 tokens.
+  const bool use_tc = kernel == 2 || (kernel == 0 && M > 32);
+  return use_tc ? twell_pack_tc(x, w, bias, packed, M, D, H, cf, st)
+                : twell_pack_small(x, w, bias, packed, M, D, H, cf, st);
 }
+
+int b200_twell_pack(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                    int64_t D, int64_t H, int cf, void* stream) {
+  return b200_twell_pack_select(x, w, bias, packed, M, D, H, cf, 0, stream);
+}
+
+int b200_twell_pack_tc_status(void) { return twell_pack_tc_status(); }
 
 int b200_twell_gated_t2d(const void* x, const void* packed, const void* up, const void* down,
                          void* out, int64_t M, int64_t D, int64_t H, int cf, uint32_t flags,

@@ -19,9 +19,13 @@
 //   hyb_spmm_t_kernel        out[j,:] = sum over rows of value(row, j) * B[row,:]
 //                            (the transposed products dK, dG, dV of custom_op.cpp:261-269)
 //   hyb_ell_spmm_raw_kernel  row-ELL x dense (ell_spmm_raw, custom_op.cpp:313)
+#include <cooperative_groups.h>
+
 #include <initializer_list>
 
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace b200 {
 namespace {
@@ -212,9 +216,14 @@ __global__ void hyb_fill_kernel(const uint32_t* __restrict__ P, int M, int tiles
 }
 
 // ---- transposed products ----------------------------------------------------
-// One CTA per column j, one warp per 256-column slice of D.  Entries of the column
-// list are taken in batches; lane q of each warp fetches entry q, values are
-// broadcast by shuffle.  NSRC value arrays share one pass over B's rows.
+// One cluster of kSplitT CTAs per column j, one warp per 256-column slice of D.  The
+// cluster's CTAs take the column's entry batches round-robin (a hot neuron's long list
+// is spread over kSplitT SMs); lane q of each warp fetches entry q of a batch, values
+// are broadcast by shuffle.  Column sums are pushed to the CTA that owns that slice of D
+// through distributed shared memory and added in rank order.  NSRC value arrays share
+// one pass over B's rows.
+constexpr int kSplitT = 8;
+
 template <int NI, int NSRC>
 __global__ void __launch_bounds__(NI * 32)
 hyb_spmm_t_kernel(const uint32_t* __restrict__ V0, const uint32_t* __restrict__ V1,
@@ -223,7 +232,12 @@ hyb_spmm_t_kernel(const uint32_t* __restrict__ V0, const uint32_t* __restrict__ 
                   __nv_bfloat16* __restrict__ out0, __nv_bfloat16* __restrict__ out1, int cap) {
   constexpr int D = NI * 256;
   constexpr int BATCH = 8;
-  const int j = blockIdx.x;
+  constexpr int COLS = D / kSplitT;  // columns finished by each CTA of the cluster
+  __shared__ __align__(16) float inbox[NSRC][kSplitT][COLS];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int j = blockIdx.x / kSplitT;
+  const int crank = blockIdx.x % kSplitT;
+  cluster.barrier_arrive();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int beg = col_start[j], end = min(col_start[j + 1], cap);
   float acc0[8], acc1[8];
@@ -231,7 +245,7 @@ hyb_spmm_t_kernel(const uint32_t* __restrict__ V0, const uint32_t* __restrict__ 
   for (int e = 0; e < 8; ++e) acc0[e] = acc1[e] = 0.f;
   const __nv_bfloat16* b_lane = Bm + warp * 256 + lane * 8;
 
-  for (int e0 = beg; e0 < end; e0 += BATCH) {
+  for (int e0 = beg + crank * BATCH; e0 < end; e0 += kSplitT * BATCH) {
     int my_row = 0;
     float my_v0 = 0.f, my_v1 = 0.f;
     if (lane < BATCH && e0 + lane < end) {
@@ -264,16 +278,33 @@ hyb_spmm_t_kernel(const uint32_t* __restrict__ V0, const uint32_t* __restrict__ 
       }
     }
   }
-  __nv_bfloat162 o[4];
+
+  cluster.barrier_wait();  // every CTA of the cluster is running: remote stores are safe
+  {
+    const int c = warp * 256 + lane * 8;
+    const int owner = c / COLS, off = c - owner * COLS;
+    float* d0 = cluster.map_shared_rank(&inbox[0][crank][off], owner);
+    *reinterpret_cast<float4*>(d0) = make_float4(acc0[0], acc0[1], acc0[2], acc0[3]);
+    *reinterpret_cast<float4*>(d0 + 4) = make_float4(acc0[4], acc0[5], acc0[6], acc0[7]);
+    if (NSRC == 2) {
+      float* d1 = cluster.map_shared_rank(&inbox[NSRC - 1][crank][off], owner);
+      *reinterpret_cast<float4*>(d1) = make_float4(acc1[0], acc1[1], acc1[2], acc1[3]);
+      *reinterpret_cast<float4*>(d1 + 4) = make_float4(acc1[4], acc1[5], acc1[6], acc1[7]);
+    }
+  }
+  cluster.sync();
+  for (int c = threadIdx.x * 2; c < COLS; c += NI * 32 * 2) {
 #pragma unroll
-  for (int p = 0; p < 4; ++p) o[p] = __floats2bfloat162_rn(acc0[2 * p], acc0[2 * p + 1]);
-  *reinterpret_cast<uint4*>(out0 + (size_t)j * D + warp * 256 + lane * 8) =
-      *reinterpret_cast<uint4*>(o);
-  if (NSRC == 2) {
+    for (int sI = 0; sI < NSRC; ++sI) {
+      float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-    for (int p = 0; p < 4; ++p) o[p] = __floats2bfloat162_rn(acc1[2 * p], acc1[2 * p + 1]);
-    *reinterpret_cast<uint4*>(out1 + (size_t)j * D + warp * 256 + lane * 8) =
-        *reinterpret_cast<uint4*>(o);
+      for (int r = 0; r < kSplitT; ++r) {
+        s0 += inbox[sI][r][c];
+        s1 += inbox[sI][r][c + 1];
+      }
+      __nv_bfloat16* o = (sI == 0 ? out0 : out1) + (size_t)j * D + crank * COLS + c;
+      *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(s0, s1);
+    }
   }
 }
 
@@ -314,11 +345,23 @@ template <int NSRC>
 int spmm_t_dispatch(int ni, int H, const uint32_t* v0, const uint32_t* v1, const int* col_start,
                     const int* csc_row, const int* csc_pos, const __nv_bfloat16* Bm,
                     __nv_bfloat16* o0, __nv_bfloat16* o1, int cap, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)H * kSplitT, 1, 1);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kSplitT;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaSuccess;
   switch (ni) {
-#define B200_CASE(N)                                                                          \
-  case N:                                                                                     \
-    hyb_spmm_t_kernel<N, NSRC><<<H, N * 32, 0, st>>>(v0, v1, col_start, csc_row, csc_pos, Bm, \
-                                                      o0, o1, cap);                           \
+#define B200_CASE(N)                                                                         \
+  case N:                                                                                    \
+    cfg.blockDim = dim3(N * 32, 1, 1);                                                       \
+    e = cudaLaunchKernelEx(&cfg, hyb_spmm_t_kernel<N, NSRC>, v0, v1, col_start, csc_row,     \
+                           csc_pos, Bm, o0, o1, cap);                                        \
     break;
     B200_CASE(1) B200_CASE(2) B200_CASE(3) B200_CASE(4) B200_CASE(5) B200_CASE(6) B200_CASE(7)
     B200_CASE(8) B200_CASE(9) B200_CASE(10) B200_CASE(11) B200_CASE(12) B200_CASE(13)
@@ -328,7 +371,9 @@ int spmm_t_dispatch(int ni, int H, const uint32_t* v0, const uint32_t* v1, const
       return fail(B200_EUNSUPPORTED, "b200_hybrid_spmm_t: D = %d is not compiled (256..4096)",
                   ni * 256);
   }
-  return check_launch("b200_hybrid_spmm_t");
+  if (e != cudaSuccess)
+    return fail(B200_ECUDA, "b200_hybrid_spmm_t: launch: %s", cudaGetErrorString(e));
+  return B200_OK;
 }
 
 int check_all(const char* fn, std::initializer_list<const void*> ptrs) {
