@@ -56,6 +56,8 @@ def parse():
     ap.add_argument("--d-ff", type=int, default=D_FF)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--eager-collectives", action="store_true",
+                    help="multi-rank: launch the step eagerly instead of as one CUDA graph")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch eagerly instead of replaying a CUDA graph (for profilers)")
     return ap.parse_args()
@@ -238,10 +240,9 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    # Multi-rank steps are launched eagerly: a step captured together with its NCCL
-    # all-reduces stalled on this software stack (2 ranks, no error raised), so graphs are
-    # used only where the step has no collective.
-    graphed = not args.no_graph and not dist_on
+    # Multi-rank steps are captured with their NCCL all-reduces inside the graph
+    # (--eager-collectives launches them eagerly instead).
+    graphed = not args.no_graph and (not dist_on or not args.eager_collectives)
     run_step = capture(step, device).replay if graphed else step
     ms_step = time_replays(run_step, args.steps, args.warmup, device, dist_on)
     clocks = sampler.stop() if rank == 0 else None
@@ -338,8 +339,14 @@ def run_ours(args):
     if rank == 0:
         print(json.dumps(result))
     if dist_on:
+        torch.cuda.synchronize(device)
         dist.barrier()
-        dist.destroy_process_group()
+        # Tearing the NCCL communicator down while captured graphs still hold its kernels
+        # stalled on this stack: every rank has finished and flushed, so leave without the
+        # collective teardown.
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def run_e2e(args, layers, x, device, dist_on):

@@ -22,6 +22,8 @@ int twell_pack_small(const void* x, const void* w, const float* bias, void* pack
                      int64_t D, int64_t H, int cf, cudaStream_t stream);
 int twell_pack_tc(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                   int64_t D, int64_t H, int cf, cudaStream_t stream);
+int twell_pack_tc_splitk(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                         int64_t D, int64_t H, int cf, cudaStream_t stream);
 int twell_pack_tc_status();
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
@@ -78,7 +80,7 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
                            int64_t M, int64_t D, int64_t H, int cf, int kernel, void* stream) {
   const char* fn = "b200_twell_pack";
   B200_TRY(check_dims(fn, M, D, H, cf));
-  if (kernel < 0 || kernel > 2) return fail(B200_EINVAL, "%s: kernel must be 0, 1 or 2", fn);
+  if (kernel < 0 || kernel > 3) return fail(B200_EINVAL, "%s: kernel must be 0..3", fn);
   if (M == 0) return B200_OK;
   B200_TRY(check_ptr(fn, "x", x));
   B200_TRY(check_ptr(fn, "w", w));
@@ -89,6 +91,7 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
   // Up to one 32-token tile the weight stream is read once and the split-k mma.sync
   // kernel is HBM-bound; beyond that the tcgen05 kernel reuses each weight tile for up
   // to 128 tokens.
+  if (kernel == 3) return twell_pack_tc_splitk(x, w, bias, packed, M, D, H, cf, st);
   const bool use_tc = kernel == 2 || (kernel == 0 && M > 32);
   return use_tc ? twell_pack_tc(x, w, bias, packed, M, D, H, cf, st)
                 : twell_pack_small(x, w, bias, packed, M, D, H, cf, st);

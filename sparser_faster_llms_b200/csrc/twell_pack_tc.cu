@@ -23,9 +23,12 @@
 // Replaces mm_wgmma_nt_kernel (custom_models/twell_modules/matmul_d2t.cu:287-709):
 // wgmma -> tcgen05.mma, register accumulators -> TMEM, multicast TMA -> per-CTA TMA,
 // shared-memory atomics in the epilogue -> ballot/popc.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace b200 {
 namespace {
@@ -36,6 +39,13 @@ constexpr int kThreadsTc = 192;             // warp 0 producer, warp 1 mma, warp
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ int g_tc_error = 0;
+#ifdef B200_TRACE
+__device__ unsigned long long g_trace_tc[16];
+__device__ __forceinline__ unsigned long long gtime_tc() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TRACE_TC(i, cond) do { if (blockIdx.x == 5 && (cond)) g_trace_tc[i] = gtime_tc(); } while (0)
+#else
+#define TRACE_TC(i, cond)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -290,6 +300,201 @@ twell_pack_tc_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Decode variant (M <= 32): the same TMA -> tcgen05 pipeline, with the reduction
+// dimension split over a cluster of CL CTAs so that (H/256)*CL CTAs stream W_gate
+// concurrently.  CTA `crank` multiplies all 256 neurons of the tile by its slice of D for
+// up to 32 tokens; the partial accumulators leave TMEM through registers and are pushed
+// (distributed shared memory) to the CTA that finalises each token, which adds the CL
+// partials in rank order and compacts with ballot / popc.
+// grid = ((H/256) * CL, ceil(M / 32)), cluster = CL.
+// Dynamic shared memory: STAGES x (A0 | A1 | B) | partial sums [32][kPartStrideTc] fp32.
+// ---------------------------------------------------------------------------
+constexpr int kTokDecode = 32;
+constexpr int kPartStrideTc = kTileN + 4;
+
+template <int CL, int STAGES>
+__global__ void __launch_bounds__(kThreadsTc, CL >= 8 ? 2 : 1)
+twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                            const __grid_constant__ CUtensorMap tmap_x,
+                            const float* __restrict__ bias, uint32_t* __restrict__ packed, int M,
+                            int D, int slab_w, int row_words) {
+  constexpr int NTOK = kTokDecode;
+  constexpr int TOK = NTOK / CL;  // tokens finalised by this CTA
+  constexpr int kBTileBytes = NTOK * 128;
+  constexpr int kStageBytes = 2 * kATileBytes + kBTileBytes;
+  constexpr uint32_t kTmemCols = 2 * NTOK;
+  constexpr uint32_t kIdesc = umma_idesc(128, NTOK);
+  constexpr int EPT = TOK * kTileN / 128;  // elements per epilogue thread in the final pass
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* part = reinterpret_cast<float*>(smem + (size_t)STAGES * kStageBytes);
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_s;
+  __shared__ int cnt_chunk[TOK][8];
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int crank = (int)cluster.block_rank();
+  cluster.barrier_arrive();  // matched by barrier_wait() before the first remote store
+  TRACE_TC(0, threadIdx.x == 0);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / CL;
+  const int m0 = blockIdx.y * NTOK;
+  const int kc = D / CL;
+  const int ksteps = kc / kStageK;
+  const int k_base = crank * kc;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+          abort_s = 1;
+          atomicExch(&g_tc_error, 1);
+          break;
+        }
+        unsigned char* st = smem + (size_t)s * kStageBytes;
+        mbar_expect_tx(&full_bar[s], (uint32_t)kStageBytes);
+        const int kcoord = k_base + k * kStageK;
+        tma_load_2d(st, &tmap_w, kcoord, tile * kTileN, &full_bar[s]);
+        tma_load_2d(st + kATileBytes, &tmap_w, kcoord, tile * kTileN + 128, &full_bar[s]);
+        tma_load_2d(st + 2 * kATileBytes, &tmap_x, kcoord, m0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], phase)) {
+          abort_s = 1;
+          atomicExch(&g_tc_error, 2);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(smem + (size_t)s * kStageBytes);
+        const uint64_t da0 = umma_desc(a0), da1 = umma_desc(a0 + kATileBytes),
+                       db = umma_desc(a0 + 2 * kATileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kStageK / 16; ++kk) {
+          const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, da0 + 2 * kk, db + 2 * kk, kIdesc, acc);
+          umma_bf16(tmem_base + NTOK, da1 + 2 * kk, db + 2 * kk, kIdesc, acc);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (!abort_s) umma_commit(&acc_bar);
+    }
+  } else {
+    // ---- epilogue part 1: TMEM -> registers -> owner CTA's shared memory ----
+    const int q = warp & 3;
+    TRACE_TC(1, threadIdx.x == 64);
+    bool ok = mbar_wait(&acc_bar, 0u);
+    if (!ok) {
+      abort_s = 1;
+      atomicExch(&g_tc_error, 3);
+    }
+    TRACE_TC(2, threadIdx.x == 64);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    cluster.barrier_wait();  // every CTA of the cluster is running
+    if (ok) {
+      const int nl = q * 32 + lane;  // neuron inside the tile (accumulator 0); +128 for 1
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+      float v0[32], v1[32];
+      tmem_ld32(lane_addr, v0);
+      tmem_ld32(lane_addr + (uint32_t)NTOK, v1);
+#pragma unroll
+      for (int c = 0; c < NTOK; ++c) {
+        const int owner = c / TOK, tl = c % TOK;
+        float* dst = cluster.map_shared_rank(part, owner) +
+                     (size_t)(crank * TOK + tl) * kPartStrideTc + nl;
+        dst[0] = v0[c];
+        dst[128] = v1[c];
+      }
+    }
+  }
+  if (warp < 2) cluster.barrier_wait();  // pair the early arrive for the non-epilogue warps
+
+  TRACE_TC(3, threadIdx.x == 64);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  cluster.sync();  // all partials delivered (every thread of every CTA takes part)
+  TRACE_TC(4, threadIdx.x == 64);
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+  if (warp < 2 || abort_s) return;
+
+  // ---- epilogue part 2: this CTA finalises tokens [crank*TOK, (crank+1)*TOK) ----
+  const int et = threadIdx.x - 64;
+  const int neuron0 = tile * kTileN;
+  float z[EPT];
+  uint32_t mask[EPT];
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int e = et + i * 128;
+    const int tl = e / kTileN, nl = e % kTileN;
+    const int tok = crank * TOK + tl;
+    float v = 0.f;
+#pragma unroll
+    for (int r = 0; r < CL; ++r) v += part[(size_t)(r * TOK + tl) * kPartStrideTc + nl];
+    if (bias != nullptr) v += bias[neuron0 + nl];
+    const bool keep = (v > 0.f) && (m0 + tok < M);
+    z[i] = v;
+    mask[i] = __ballot_sync(0xffffffffu, keep);
+    if (lane == 0) cnt_chunk[tl][nl / 32] = __popc(mask[i]);
+  }
+  epi_barrier();
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int e = et + i * 128;
+    const int tl = e / kTileN, nl = e % kTileN;
+    const int tok = crank * TOK + tl;
+    if (m0 + tok >= M) continue;
+    uint32_t* slab = packed + (size_t)(m0 + tok) * row_words + (size_t)tile * slab_w;
+    int before = 0, total = 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int v = cnt_chunk[tl][c];
+      if (c < nl / 32) before += v;
+      total += v;
+    }
+    if (nl == 0) slab[0] = (uint32_t)total;
+    const int slot = before + __popc(mask[i] & lanemask_lt());
+    if (((mask[i] >> lane) & 1u) && slot < slab_w - 1)
+      slab[1 + slot] = (uint32_t)(neuron0 + nl) | (bf16_bits(z[i]) << 16);
+  }
+  TRACE_TC(5, threadIdx.x == 64);
+}
+
 // ---- host side -------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -345,7 +550,49 @@ int launch_tc(const void* x, const void* w, const float* bias, void* packed, int
   return check_launch("b200_twell_pack (tcgen05)");
 }
 
+template <int CL, int STAGES>
+int launch_tc_splitk(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                     int64_t D, int64_t H, int cf, cudaStream_t stream) {
+  CUtensorMap map_w, map_x;
+  if (int rc = make_map(&map_w, w, H, D, 128)) return rc;
+  if (int rc = make_map(&map_x, x, M, D, kTokDecode)) return rc;
+  const size_t smem = (size_t)STAGES * (2 * kATileBytes + kTokDecode * 128) +
+                      (size_t)kTokDecode * kPartStrideTc * sizeof(float) + 1024;
+  auto kern = twell_pack_tc_splitk_kernel<CL, STAGES>;
+  static size_t granted[64] = {0};
+  if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_pack")) return rc;
+  const int slab_w = kTileN / cf;
+  const int tiles = (int)(H / kTileN);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(tiles * CL), (unsigned)((M + kTokDecode - 1) / kTokDecode), 1);
+  cfg.blockDim = dim3(kThreadsTc, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, bias,
+                                     static_cast<uint32_t*>(packed), (int)M, (int)D, slab_w,
+                                     tiles * slab_w);
+  if (e != cudaSuccess)
+    return fail(B200_ECUDA, "b200_twell_pack (tcgen05 split-k): launch: %s",
+                cudaGetErrorString(e));
+  return B200_OK;
+}
+
 }  // namespace
+
+// Decode path on the tensor cores: split-k over a cluster of 4 CTAs.
+int twell_pack_tc_splitk(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                         int64_t D, int64_t H, int cf, cudaStream_t stream) {
+  if (getenv("B200_TCS8") != nullptr && D % 512 == 0)
+    return launch_tc_splitk<8, 2>(x, w, bias, packed, M, D, H, cf, stream);
+  return launch_tc_splitk<4, 5>(x, w, bias, packed, M, D, H, cf, stream);
+}
 
 // Large-M path.  Needs D % 64 == 0 (guaranteed by D % 256 == 0).
 int twell_pack_tc(const void* x, const void* w, const float* bias, void* packed, int64_t M,
@@ -363,4 +610,7 @@ int twell_pack_tc_status() {
   return v;
 }
 
+#ifdef B200_TRACE
+extern "C" void b200_debug_trace_tc(unsigned long long* host) { cudaMemcpyFromSymbol(host, g_trace_tc, sizeof(unsigned long long) * 16); }
+#endif
 }  // namespace b200
