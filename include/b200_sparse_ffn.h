@@ -69,10 +69,12 @@ int b200_twell_pack(const void* x, const void* w, const float* bias, void* packe
 
 /*
  * Same as b200_twell_pack with the kernel family chosen by the caller:
- *   kernel 0 = automatic (M <= 32: split-k cluster kernel on mma.sync, HBM-bound;
- *              M > 32: tcgen05 / TMEM / TMA kernel),
- *   kernel 1 = split-k cluster kernel, kernel 2 = tcgen05 kernel.
- * Both produce identical slab bytes on exact-arithmetic inputs.  No reference
+ *   kernel 0 = automatic (M <= 16: split-k cluster kernel on mma.sync; 17..32: tcgen05
+ *              split-k cluster kernel; M > 32: tcgen05 / TMEM / TMA tile kernel),
+ *   kernel 1 = mma.sync split-k cluster kernel (any M),
+ *   kernel 2 = tcgen05 tile kernel (64 or 128 tokens per CTA tile),
+ *   kernel 3 = tcgen05 split-k cluster kernel (32 tokens per tile, D split 4 ways).
+ * All produce identical slab bytes on exact-arithmetic inputs.  No reference
  * counterpart (the reference has one WGMMA kernel, matmul_d2t.cu:287-709).
  */
 int b200_twell_pack_select(const void* x, const void* w, const float* bias, void* packed,

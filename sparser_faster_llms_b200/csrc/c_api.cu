@@ -91,7 +91,11 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
   // Up to one 32-token tile the weight stream is read once and the split-k mma.sync
   // kernel is HBM-bound; beyond that the tcgen05 kernel reuses each weight tile for up
   // to 128 tokens.
-  if (kernel == 3) return twell_pack_tc_splitk(x, w, bias, packed, M, D, H, cf, st);
+  // Measured on B200 (D 2048, H 8192): up to 16 tokens the mma.sync cluster kernel is
+  // fastest (9.6-9.9 us vs 11.7-12.4); at 17..32 tokens its mma work per CTA grows and the
+  // tcgen05 split-k kernel wins (12.5 vs 13.9 us).
+  if (kernel == 3 || (kernel == 0 && M > 16 && M <= 32))
+    return twell_pack_tc_splitk(x, w, bias, packed, M, D, H, cf, st);
   const bool use_tc = kernel == 2 || (kernel == 0 && M > 32);
   return use_tc ? twell_pack_tc(x, w, bias, packed, M, D, H, cf, st)
                 : twell_pack_small(x, w, bias, packed, M, D, H, cf, st);

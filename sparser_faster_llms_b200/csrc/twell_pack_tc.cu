@@ -39,13 +39,6 @@ constexpr int kThreadsTc = 192;             // warp 0 producer, warp 1 mma, warp
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ int g_tc_error = 0;
-#ifdef B200_TRACE
-__device__ unsigned long long g_trace_tc[16];
-__device__ __forceinline__ unsigned long long gtime_tc() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define TRACE_TC(i, cond) do { if (blockIdx.x == 5 && (cond)) g_trace_tc[i] = gtime_tc(); } while (0)
-#else
-#define TRACE_TC(i, cond)
-#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -339,7 +332,6 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
   cg::cluster_group cluster = cg::this_cluster();
   const int crank = (int)cluster.block_rank();
   cluster.barrier_arrive();  // matched by barrier_wait() before the first remote store
-  TRACE_TC(0, threadIdx.x == 0);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x / CL;
@@ -414,13 +406,11 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
   } else {
     // ---- epilogue part 1: TMEM -> registers -> owner CTA's shared memory ----
     const int q = warp & 3;
-    TRACE_TC(1, threadIdx.x == 64);
     bool ok = mbar_wait(&acc_bar, 0u);
     if (!ok) {
       abort_s = 1;
       atomicExch(&g_tc_error, 3);
     }
-    TRACE_TC(2, threadIdx.x == 64);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     cluster.barrier_wait();  // every CTA of the cluster is running
     if (ok) {
@@ -441,10 +431,8 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
   if (warp < 2) cluster.barrier_wait();  // pair the early arrive for the non-epilogue warps
 
-  TRACE_TC(3, threadIdx.x == 64);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   cluster.sync();  // all partials delivered (every thread of every CTA takes part)
-  TRACE_TC(4, threadIdx.x == 64);
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
@@ -473,6 +461,18 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
     if (lane == 0) cnt_chunk[tl][nl / 32] = __popc(mask[i]);
   }
   epi_barrier();
+  if (et < TOK) {  // counts -> exclusive prefix over the 8 chunks of this token, count word
+    int run = 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int v = cnt_chunk[et][c];
+      cnt_chunk[et][c] = run;
+      run += v;
+    }
+    const int tok = m0 + crank * TOK + et;
+    if (tok < M) packed[(size_t)tok * row_words + (size_t)tile * slab_w] = (uint32_t)run;
+  }
+  epi_barrier();
 #pragma unroll
   for (int i = 0; i < EPT; ++i) {
     const int e = et + i * 128;
@@ -480,19 +480,10 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int tok = crank * TOK + tl;
     if (m0 + tok >= M) continue;
     uint32_t* slab = packed + (size_t)(m0 + tok) * row_words + (size_t)tile * slab_w;
-    int before = 0, total = 0;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const int v = cnt_chunk[tl][c];
-      if (c < nl / 32) before += v;
-      total += v;
-    }
-    if (nl == 0) slab[0] = (uint32_t)total;
-    const int slot = before + __popc(mask[i] & lanemask_lt());
+    const int slot = cnt_chunk[tl][nl / 32] + __popc(mask[i] & lanemask_lt());
     if (((mask[i] >> lane) & 1u) && slot < slab_w - 1)
       slab[1 + slot] = (uint32_t)(neuron0 + nl) | (bf16_bits(z[i]) << 16);
   }
-  TRACE_TC(5, threadIdx.x == 64);
 }
 
 // ---- host side -------------------------------------------------------------
@@ -589,8 +580,6 @@ int launch_tc_splitk(const void* x, const void* w, const float* bias, void* pack
 // Decode path on the tensor cores: split-k over a cluster of 4 CTAs.
 int twell_pack_tc_splitk(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                          int64_t D, int64_t H, int cf, cudaStream_t stream) {
-  if (getenv("B200_TCS8") != nullptr && D % 512 == 0)
-    return launch_tc_splitk<8, 2>(x, w, bias, packed, M, D, H, cf, stream);
   return launch_tc_splitk<4, 5>(x, w, bias, packed, M, D, H, cf, stream);
 }
 
@@ -610,7 +599,4 @@ int twell_pack_tc_status() {
   return v;
 }
 
-#ifdef B200_TRACE
-extern "C" void b200_debug_trace_tc(unsigned long long* host) { cudaMemcpyFromSymbol(host, g_trace_tc, sizeof(unsigned long long) * 16); }
-#endif
 }  // namespace b200

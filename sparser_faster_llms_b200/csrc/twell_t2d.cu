@@ -38,7 +38,10 @@ namespace {
 
 constexpr int kMaxTiles = 256;  // H <= 65536
 constexpr int kChunk = 256;     // entries staged in shared memory at a time
-constexpr int kDepth = 8;       // entries per batch (row loads in flight per lane: 2x gated)
+#ifndef B200_T2D_DEPTH
+#define B200_T2D_DEPTH 8
+#endif
+constexpr int kDepth = B200_T2D_DEPTH;  // entries per batch (row loads in flight per lane: 2x gated)
 constexpr int kStageWords = 4096;  // slab rows up to this many words are staged in shared memory
 
 __device__ __forceinline__ uint4 ldg_nc(const void* p) {
