@@ -294,7 +294,11 @@ def run_ours(args):
                    "ms_per_layer": ms_step / L,
                    "dense_cublas_bf16_ms_per_step": ms_dense,
                    "ffn_algorithmic_gbs": ffn_bytes / (ms_step / L * 1e-3) / 1e9},
-        "roofline": {"bound": "hbm", "kernel": "twell_pack_kernel", "achieved": achieved,
+        "roofline": {"bound": "hbm",
+                     "kernel": ("twell_pack_kernel" if B <= 16 else
+                                "twell_pack_tc_splitk_kernel" if B <= 32 else
+                                "twell_pack_tc_kernel"),
+                     "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": achieved / peak,
                      # ncu dram__bytes_read+write per launch = 1.00 x the algorithmic bytes

@@ -586,6 +586,9 @@ int twell_pack_tc_splitk(const void* x, const void* w, const float* bias, void* 
 // Large-M path.  Needs D % 64 == 0 (guaranteed by D % 256 == 0).
 int twell_pack_tc(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                   int64_t D, int64_t H, int cf, cudaStream_t stream) {
+  // 256-token tiles raise the flops per byte staged through shared memory (the 128-token
+  // tile is bound by L2 -> SM bandwidth); they use all 512 TMEM columns.
+  if (M >= 1024) return launch_tc<256, 3>(x, w, bias, packed, M, D, H, cf, stream);
   if (M > 64) return launch_tc<128, 4>(x, w, bias, packed, M, D, H, cf, stream);
   return launch_tc<64, 4>(x, w, bias, packed, M, D, H, cf, stream);
 }

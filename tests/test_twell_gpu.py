@@ -342,7 +342,8 @@ def _pack_with(kernel, x, w, cf, bias=None):
 
 
 @pytest.mark.parametrize("m,d,h", [(33, 256, 256), (64, 512, 512), (65, 1024, 768),
-                                   (128, 2048, 1024), (300, 1024, 11008), (1000, 512, 2048)])
+                                   (128, 2048, 1024), (300, 1024, 11008), (1000, 512, 2048),
+                                   (1280, 512, 768)])
 @pytest.mark.parametrize("cf", [8, 2])
 def test_tcgen05_pack_kernel_bit_exact_with_oracle_and_with_cluster_kernel(m, d, h, cf):
     """Exact-arithmetic inputs: the tcgen05 / TMEM kernel, the split-k cluster kernel and the
