@@ -58,6 +58,9 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--eager-collectives", action="store_true",
                     help="multi-rank: launch the step eagerly instead of as one CUDA graph")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="multi-rank: sum the partial outputs with the library's peer-memory "
+                         "all-reduce kernel (default) or with NCCL")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch eagerly instead of replaying a CUDA graph (for profilers)")
     return ap.parse_args()
@@ -200,6 +203,27 @@ def time_replays(run, steps, warmup, device, dist_on):
     return ms / steps
 
 
+def make_peer_allreduce(args, device, dist_on):
+    """(PeerAllReduce or None, description).  Every rank takes the same branch: the outcome of
+    the symmetric-memory set-up is agreed with a MIN all-reduce before anyone uses it."""
+    if not dist_on:
+        return None, "none"
+    if args.collective == "nccl":
+        return None, "nccl all-reduce"
+    import torch.distributed as dist
+    from sparser_faster_llms_b200 import peer_allreduce
+    par, why = None, ""
+    try:
+        par = peer_allreduce.PeerAllReduce(args.batch * args.d_model * 2, device=device)
+    except Exception as exc:  # symmetric memory not available on this box
+        why = f"{type(exc).__name__}: {exc}"[:160]
+    ok = torch.tensor([1 if par is not None else 0], device=device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok.item()) == 1:
+        return par, "peer-memory all-reduce kernel (b200_peer_allreduce_bf16)"
+    return None, f"nccl all-reduce (peer all-reduce unavailable: {why or 'on another rank'})"
+
+
 def run_ours(args):
     import torch.distributed as dist
     from sparser_faster_llms_b200 import _lib, twell
@@ -224,12 +248,18 @@ def run_ours(args):
                          device=device)
     ws = (ws_buf.data_ptr(), ws_buf.numel())
 
+    par, collective = make_peer_allreduce(args, device, dist_on)
+    part = torch.empty(B, d, device=device, dtype=torch.bfloat16) if par is not None else None
+
     def step():
         for l, (g, u, dn) in enumerate(layers):
+            y = out[l] if par is None else part
             _lib.call("b200_twell_gated_mlp", device, x[l].data_ptr(), g.data_ptr(), None,
-                      u.data_ptr(), dn.data_ptr(), packed.data_ptr(), out[l].data_ptr(),
+                      u.data_ptr(), dn.data_ptr(), packed.data_ptr(), y.data_ptr(),
                       B, d, hl, 8, 0, *ws)
-            if dist_on:
+            if par is not None:
+                par.all_reduce(part, out[l])
+            elif dist_on:
                 dist.all_reduce(out[l])
 
     def pack_only():
@@ -288,7 +318,7 @@ def run_ours(args):
                    "layers": L, "d_model": d, "d_ff": args.d_ff, "batch": B,
                    "d_ff_shard": [h0, h1], "parallelism": f"dff_shard{world}",
                    "l2": "weights (2.8 GB) exceed L2; no flush needed",
-                   "cuda_graph": graphed,
+                   "cuda_graph": graphed, "collective": collective,
                    "nnz_per_token_last_layer": nnz_per_token,
                    "active_union_last_layer": union,
                    "ms_per_layer": ms_step / L,
@@ -305,7 +335,7 @@ def run_ours(args):
                      # (profiles/decode_ffn_batch32_pack_and_contraction.md), scaled to this launch
                      "traffic": float(pack_bytes),
                      "us_per_launch": ms_pack * 1e3, "algorithmic_bytes": pack_bytes},
-        "gpu_launches": args.steps * L * 2,
+        "gpu_launches": args.steps * L * (3 if par is not None else 2),
         "clocks": clocks,
     }
 
@@ -337,7 +367,10 @@ def run_ours(args):
         result["config"]["other_batches"] = others
 
     if not args.no_e2e:
-        result["e2e"] = run_e2e(args, layers, x, device, dist_on)
+        result["e2e"] = run_e2e(args, layers, x, device, dist_on, par)
+    if par is not None:
+        # non-zero: a bounded wait on a peer gave up somewhere in the run (results invalid)
+        result["config"]["peer_allreduce_status"] = par.status()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(args, sample_layers=2, reps=3)
     if rank == 0:
@@ -353,7 +386,7 @@ def run_ours(args):
         os._exit(0)
 
 
-def run_e2e(args, layers, x, device, dist_on):
+def run_e2e(args, layers, x, device, dist_on, par=None):
     """The same stack through the public modules (TwELLGatedMLP, or the d_ff-sharded module
     on several ranks) run by GraphedFFNStack: every step copies the inputs from pinned host
     memory, runs all layers and reads the last layer's output back to the host."""
@@ -362,6 +395,7 @@ def run_e2e(args, layers, x, device, dist_on):
     L, B, d = args.layers, args.batch, args.d_model
     if dist_on:
         mods = [sharded.ShardedTwELLGatedMLP(1000 + l, g, u, dn, presharded=True,
+                                             peer_allreduce=par,
                                              preallocate_shared_hidden_state=True)
                 for l, (g, u, dn) in enumerate(layers)]
     else:

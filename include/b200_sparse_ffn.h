@@ -203,6 +203,29 @@ int b200_hybrid_ell_spmm_raw(const void* ell_vals, const void* ell_cols, const i
                              const void* b, void* c, int64_t M, int64_t K, int64_t N,
                              int64_t ell_stride, int64_t overflow_threshold, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Sum all-reduce of the d_ff-sharded FFN output over peer-mapped memory (no reference
+ * counterpart: the reference is data parallel only).  Every rank owns one symmetric
+ * block of b200_peer_allreduce_block_bytes(max_bytes) bytes, zero-filled once, and
+ * knows the device address of every rank's block (peer-mapped: CUDA IPC, VMM or
+ * torch symmetric memory).  One call = one kernel per rank: push the local bf16
+ * tensor into every peer's inbox as 8-byte {payload, call epoch} words (no fence, no
+ * separate flag), poll the own inbox with a bounded wait, sum in rank order into `out`
+ * (identical bits on every rank).  All ranks must issue the same sequence of calls
+ * (same n_elems) on their streams; the launch may be captured in a CUDA graph.
+ * ------------------------------------------------------------------------ */
+size_t b200_peer_allreduce_block_bytes(int64_t max_bytes);
+
+/* peer_blocks: host array of `world` device pointers (entry `rank` = this rank's block).
+ * n_elems: multiple of 8, n_elems*2 <= max_bytes.  world <= 8. */
+int b200_peer_allreduce_bf16(const void* local_in, void* out, int64_t n_elems,
+                             void* const* peer_blocks, int rank, int world,
+                             int64_t block_bytes, void* stream);
+
+/* 0, or 0x100 + peer rank if a wait for that peer gave up; -1 if unreadable.  Reads and
+ * clears the word; synchronises the device. */
+int b200_peer_allreduce_status(void* my_block);
+
 /*
  * Gated contraction for hosts that may not allocate device memory (no counterpart
  * in the reference).  Same arguments and result as b200_twell_gated_t2d, minus the

@@ -53,6 +53,10 @@ _PROTOTYPES = {
     "b200_hybrid_spmm_t": (c_int, [c_void_p] * 5 + [c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                                     c_int64, c_void_p]),
     "b200_hybrid_ell_spmm_raw": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_void_p]),
+    "b200_peer_allreduce_block_bytes": (c_size_t, [c_int64]),
+    "b200_peer_allreduce_bf16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int,
+                                         c_int64, c_void_p]),
+    "b200_peer_allreduce_status": (c_int, [c_void_p]),
     "b200_twell_gated_t2d_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_int64, c_int64, c_int64, c_int, c_uint32,
                                              c_void_p]),

@@ -58,10 +58,13 @@ class ShardedTwELLGatedMLP(nn.Module):
     def __init__(self, layer_number: int, GATE: torch.Tensor, UP: torch.Tensor,
                  DOWN: torch.Tensor, *, process_group=None, rank: int | None = None,
                  world_size: int | None = None, presharded: bool = False,
-                 reduce_dtype: torch.dtype | None = None,
+                 reduce_dtype: torch.dtype | None = None, peer_allreduce=None,
                  local_factory: Callable[..., nn.Module] | None = None, **twell_kwargs):
         super().__init__()
         self.process_group = process_group
+        # optional sparser_faster_llms_b200.peer_allreduce.PeerAllReduce shared by all layers:
+        # one peer-memory kernel instead of an NCCL all-reduce (bf16 sum, rank order)
+        self.peer_allreduce = peer_allreduce
         if world_size is None:
             world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
         if rank is None:
@@ -82,6 +85,8 @@ class ShardedTwELLGatedMLP(nn.Module):
 
     def forward(self, A: torch.Tensor) -> torch.Tensor:
         y = self.local(A)
+        if self.world_size > 1 and self.peer_allreduce is not None:
+            return self.peer_allreduce.all_reduce(y.contiguous())
         if self.world_size > 1:
             if self.reduce_dtype is not None and self.reduce_dtype != y.dtype:
                 acc = y.to(self.reduce_dtype)

@@ -30,7 +30,7 @@ class GraphedFFNStack:
         self.mlps = list(mlps)
         if not self.mlps:
             raise ValueError("need at least one module")
-        first = self.mlps[0]
+        first = getattr(self.mlps[0], "local", self.mlps[0])  # d_ff-sharded modules wrap one
         dev = torch.device(device) if device is not None else first.GATE.device
         if dev.type != "cuda":
             raise RuntimeError("GraphedFFNStack needs CUDA modules (there is no CPU path)")
