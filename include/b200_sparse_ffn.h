@@ -204,6 +204,49 @@ int b200_hybrid_ell_spmm_raw(const void* ell_vals, const void* ell_cols, const i
                              int64_t ell_stride, int64_t overflow_threshold, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Hybrid contraction for large token counts: rows whose gate has more than
+ * nnz_threshold positives, or whose slab overflowed in some tile, are computed
+ * as dense tcgen05 GEMMs (gate and up recomputed densely, so nothing is lost to
+ * slab capacity); all other rows run on the gather kernel of b200_twell_gated_t2d.
+ * At most dense_cap rows (ascending row order) take the dense route.
+ * Replaces the dense tail of the reference's hybrid format (hybrid_sp.cu:516-576:
+ * rows beyond the ELL width go to tail_dense and through torch::matmul); the
+ * reference's TwELL inference kernels have no such route and drop overflowed
+ * entries (matmul_gated_t2d.cu:17-169).
+ *   gate, up, down [H, D] bf16 as elsewhere; down_t [D, H] bf16 = a K-major copy of
+ *   the down projection (down_proj.weight itself) kept by the caller;
+ *   hybrid_ws: b200_twell_hybrid_workspace_bytes(M, D, H, dense_cap) bytes,
+ *   256-byte aligned, contents need not be initialised; workspace as in
+ *   b200_twell_gated_t2d.  No host synchronisation.
+ * ------------------------------------------------------------------------ */
+size_t b200_twell_hybrid_workspace_bytes(int64_t M, int64_t D, int64_t H, int64_t dense_cap);
+
+int b200_twell_gated_t2d_hybrid(const void* x, const void* packed, const void* gate,
+                                const float* gate_bias, const void* up, const void* down,
+                                const void* down_t, void* out, int64_t M, int64_t D, int64_t H,
+                                int cf, uint32_t flags, int64_t nnz_threshold, int64_t dense_cap,
+                                void* hybrid_ws, size_t hybrid_ws_bytes, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
+/* b200_twell_pack followed by b200_twell_gated_t2d_hybrid. */
+int b200_twell_gated_mlp_hybrid(const void* x, const void* gate, const float* gate_bias,
+                                const void* up, const void* down, const void* down_t,
+                                void* packed, void* out, int64_t M, int64_t D, int64_t H, int cf,
+                                uint32_t flags, int64_t nnz_threshold, int64_t dense_cap,
+                                void* hybrid_ws, size_t hybrid_ws_bytes, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
+/* counters_out[0] = rows the last call on this workspace routed to the dense path,
+ * [1] = overflowed rows left on the sparse path because dense_cap was exhausted,
+ * [2] = rows that qualified.  Synchronises the device. */
+int b200_twell_hybrid_counters(const void* hybrid_ws, int64_t M, int64_t D, int64_t H,
+                               int64_t dense_cap, int* counters_out);
+
+/* 0, or the stage (1 producer, 2 mma, 3 epilogue) of a bounded wait that gave up in the
+ * dense GEMMs; reads and clears the word; synchronises the device. */
+int b200_twell_hybrid_status(void);
+
+/* ------------------------------------------------------------------------
  * Sum all-reduce of the d_ff-sharded FFN output over peer-mapped memory (no reference
  * counterpart: the reference is data parallel only).  Every rank owns one symmetric
  * block of b200_peer_allreduce_block_bytes(max_bytes) bytes, zero-filled once, and

@@ -53,6 +53,19 @@ _PROTOTYPES = {
     "b200_hybrid_spmm_t": (c_int, [c_void_p] * 5 + [c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                                     c_int64, c_void_p]),
     "b200_hybrid_ell_spmm_raw": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_void_p]),
+    "b200_twell_hybrid_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),
+    # x, packed, gate, gate_bias, up, down, down_t, out, M, D, H, cf, flags, nnz_threshold,
+    # dense_cap, hybrid_ws, hybrid_ws_bytes, workspace, workspace_bytes, stream
+    "b200_twell_gated_t2d_hybrid": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int64, c_int,
+                                            c_uint32, c_int64, c_int64, c_void_p, c_size_t,
+                                            c_void_p, c_size_t, c_void_p]),
+    # x, gate, gate_bias, up, down, down_t, packed, out, then as above
+    "b200_twell_gated_mlp_hybrid": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int64, c_int,
+                                            c_uint32, c_int64, c_int64, c_void_p, c_size_t,
+                                            c_void_p, c_size_t, c_void_p]),
+    "b200_twell_hybrid_counters": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                           ctypes.POINTER(c_int)]),
+    "b200_twell_hybrid_status": (c_int, []),
     "b200_peer_allreduce_block_bytes": (c_size_t, [c_int64]),
     "b200_peer_allreduce_bf16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int,
                                          c_int64, c_void_p]),

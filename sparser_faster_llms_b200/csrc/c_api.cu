@@ -27,7 +27,8 @@ int twell_pack_tc_splitk(const void* x, const void* w, const float* bias, void* 
 int twell_pack_tc_status();
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
-                     void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
+                     void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream,
+                     const unsigned char* skip_rows = nullptr);
 
 // Number of SMs of the current device (cached per device ordinal).
 int sm_count() {

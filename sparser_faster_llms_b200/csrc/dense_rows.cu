@@ -1,0 +1,425 @@
+// Hybrid contraction for large token counts: dense-enough token rows leave the gather path
+// and run as dense tensor-core GEMMs; the remaining rows stay on the TwELL gather kernel.
+//
+// A token whose gate row has more positives than a threshold, or whose slab overflowed in
+// some 256-neuron tile (count > capacity, entries lost), costs more as a per-entry gather
+// of W_up / W_down rows through L2 than as three dense products.  The path is
+//   1. route:   per row, nnz and overflow from the slab count words -> flag; a single-CTA
+//               scan turns the flags into an ascending list of dense rows (at most
+//               `dense_cap`; later rows stay sparse and are counted if they were lossy),
+//   2. sparse:  the gather kernel skips flagged rows,
+//   3. gather:  Xd[i, :] = x[dense_rows[i], :],
+//   4. GEMM 1:  Hd = relu(Xd Wg^T + b) * (Xd Wu^T)   tcgen05, two TMEM accumulators per CTA
+//               (gate and up of the same 128 neurons x 128 tokens), bf16 store,
+//   5. GEMM 2:  y[dense_rows[i], :] = Hd Wd          tcgen05, K = H, A operand = Wd^T [D, H]
+//               (a K-major copy of the down projection kept by the caller), scattered store.
+// Dense rows are computed from the dense gate product, not from the slab, so rows that
+// overflowed the slab lose nothing.  The dense-row count lives on the device: grids are
+// sized for `dense_cap` and CTAs beyond the count return at once; no host synchronisation.
+//
+// Reference counterpart: the hybrid format's dense tail (hybrid_sp.cu:516-576: rows whose
+// count exceeds the ELL width go to `tail_dense` and are multiplied with torch::matmul);
+// the TwELL inference kernels themselves have no such route
+// (custom_models/twell_modules/matmul_gated_t2d.cu:17-169 drops overflowed entries).
+#include "tc_common.cuh"
+
+namespace b200 {
+
+int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
+                     const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
+                     void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream,
+                     const unsigned char* skip_rows);
+int sm_count();
+
+namespace {
+
+__device__ int g_dense_error = 0;
+
+constexpr int kDenseTok = 128;  // tokens per CTA tile of the dense GEMMs
+
+// ---- routing ----------------------------------------------------------------
+// One warp per row: flag bit 0 = nnz above the threshold, bit 1 = some tile overflowed.
+__global__ void __launch_bounds__(256)
+route_flags_kernel(const uint32_t* __restrict__ packed, int M, int tiles, int slab_w,
+                   int nnz_threshold, unsigned char* __restrict__ flags) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const uint32_t* prow = packed + (size_t)row * tiles * slab_w;
+  int nnz = 0, over = 0;
+  for (int t = lane; t < tiles; t += 32) {
+    const int c = (int)prow[(size_t)t * slab_w];
+    nnz += max(c, 0);
+    over |= (c > slab_w - 1) ? 1 : 0;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    nnz += __shfl_xor_sync(0xffffffffu, nnz, o);
+    over |= __shfl_xor_sync(0xffffffffu, over, o);
+  }
+  if (lane == 0) flags[row] = (unsigned char)((nnz > nnz_threshold ? 1 : 0) | (over ? 2 : 0));
+}
+
+// One CTA: ascending list of flagged rows, at most `cap`; rows beyond it return to the
+// sparse path.  counters[0] = dense rows, [1] = overflowed rows left on the (lossy) sparse
+// path, [2] = rows that qualified.
+__global__ void __launch_bounds__(1024)
+route_compact_kernel(unsigned char* __restrict__ flags, int M, int cap, int* __restrict__ rows,
+                     int* __restrict__ counters) {
+  __shared__ int warp_sum[32];
+  __shared__ int lossy_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int per = (M + 1023) / 1024;
+  const int r0 = tid * per, r1 = min(M, r0 + per);
+  if (tid == 0) lossy_s = 0;
+  int mine = 0;
+  for (int r = r0; r < r1; ++r) mine += flags[r] != 0;
+  int inc = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += v;
+  }
+  if (lane == 31) warp_sum[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_sum[lane], winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += v;
+    }
+    warp_sum[lane] = winc - w;  // exclusive prefix of the warp totals
+    if (lane == 31) counters[2] = winc;
+    if (lane == 31) counters[0] = min(winc, cap);
+  }
+  __syncthreads();
+  int pos = warp_sum[warp] + inc - mine;
+  int lossy = 0;
+  for (int r = r0; r < r1; ++r) {
+    const unsigned char f = flags[r];
+    if (f == 0) continue;
+    if (pos < cap) {
+      rows[pos] = r;
+    } else {
+      flags[r] = 0;  // stays on the gather path
+      lossy += (f & 2) ? 1 : 0;
+    }
+    ++pos;
+  }
+  if (lossy) atomicAdd(&lossy_s, lossy);
+  __syncthreads();
+  if (tid == 0) counters[1] = lossy_s;
+}
+
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ rows,
+                   const int* __restrict__ counters, uint4* __restrict__ xd, int vec_per_row) {
+  const int i = blockIdx.x;
+  if (i >= counters[0]) return;
+  const uint4* src = x + (size_t)rows[i] * vec_per_row;
+  uint4* dst = xd + (size_t)i * vec_per_row;
+  for (int v = threadIdx.x; v < vec_per_row; v += 256) dst[v] = __ldg(src + v);
+}
+
+// ---- dense GEMMs --------------------------------------------------------------
+// acc0[128, NTOK] = A0 tile . B^T, acc1[128, NTOK] = A1 tile . B^T over K, both in TMEM
+// (lane = output feature, column = token).
+//   DUAL:  A0 = W_gate rows, A1 = W_up rows of the same 128 neurons (grid.x = H / 128);
+//          epilogue h = relu(g + bias) * u -> out[token, neuron] (ld_out = H).
+//   !DUAL: A0 / A1 = rows [256 t, +128) and [256 t + 128, +128) of one matrix
+//          (grid.x = N_out / 256); epilogue out[row_ids[token], feature] = acc (ld_out = N_out).
+// grid.y = token tiles of the capacity; tiles at or beyond *n_rows_ptr return at once.
+template <int NTOK, int STAGES, bool DUAL>
+__global__ void __launch_bounds__(kThreadsTc, 1)
+dense_rows_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
+                       const __grid_constant__ CUtensorMap tmap_a1,
+                       const __grid_constant__ CUtensorMap tmap_b, const float* __restrict__ bias,
+                       __nv_bfloat16* __restrict__ out, const int* __restrict__ row_ids,
+                       const int* __restrict__ n_rows_ptr, int K, int ld_out) {
+  constexpr int kBTileBytes = NTOK * 128;
+  constexpr int kStageBytes = 2 * kATileBytes + kBTileBytes;
+  constexpr uint32_t kTmemCols = 2 * NTOK;
+  constexpr uint32_t kIdesc = umma_idesc(128, NTOK);
+
+  const int n_rows = *n_rows_ptr;
+  const int m0 = blockIdx.y * NTOK;
+  if (m0 >= n_rows) return;  // uniform for the CTA: nothing allocated yet
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x;
+  const int ksteps = K / kStageK;
+  const int a0_row = DUAL ? tile * 128 : tile * 256;
+  const int a1_row = DUAL ? tile * 128 : tile * 256 + 128;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+          abort_s = 1;
+          atomicExch(&g_dense_error, 1);
+          break;
+        }
+        unsigned char* st = smem + (size_t)s * kStageBytes;
+        mbar_expect_tx(&full_bar[s], (uint32_t)kStageBytes);
+        tma_load_2d(st, &tmap_a0, k * kStageK, a0_row, &full_bar[s]);
+        tma_load_2d(st + kATileBytes, DUAL ? &tmap_a1 : &tmap_a0, k * kStageK, a1_row,
+                    &full_bar[s]);
+        tma_load_2d(st + 2 * kATileBytes, &tmap_b, k * kStageK, m0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], phase)) {
+          abort_s = 1;
+          atomicExch(&g_dense_error, 2);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(smem + (size_t)s * kStageBytes);
+        const uint64_t da0 = umma_desc(a0), da1 = umma_desc(a0 + kATileBytes),
+                       db = umma_desc(a0 + 2 * kATileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kStageK / 16; ++kk) {
+          const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, da0 + 2 * kk, db + 2 * kk, kIdesc, acc);
+          umma_bf16(tmem_base + NTOK, da1 + 2 * kk, db + 2 * kk, kIdesc, acc);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (!abort_s) umma_commit(&acc_bar);
+    }
+  } else {
+    // ---- epilogue: warps 2..5 own TMEM lane quarters 2, 3, 0, 1 ----
+    const int q = warp & 3;
+    bool ok = mbar_wait(&acc_bar, 0u);
+    if (!ok) {
+      abort_s = 1;
+      atomicExch(&g_dense_error, 3);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const int f0 = a0_row + q * 32 + lane;  // output feature of accumulator 0
+    const float b0 = (DUAL && bias != nullptr) ? bias[f0] : 0.f;
+    for (int tb = 0; tb < NTOK / 32 && ok; ++tb) {
+      if (m0 + tb * 32 >= n_rows) break;
+      float v0[32], v1[32];
+      tmem_ld32(lane_addr + (uint32_t)(tb * 32), v0);
+      tmem_ld32(lane_addr + (uint32_t)(NTOK + tb * 32), v1);
+      if (DUAL) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int tok = m0 + tb * 32 + c;
+          if (tok >= n_rows) break;
+          const float g = v0[c] + b0;
+          float h = 0.f;
+          if (g > 0.f)
+            h = __bfloat162float(__float2bfloat16_rn(g)) * __bfloat162float(__float2bfloat16_rn(v1[c]));
+          out[(size_t)tok * ld_out + f0] = __float2bfloat16_rn(h);
+        }
+      } else {
+        const int t_mine = m0 + tb * 32 + lane;
+        const int rid = t_mine < n_rows ? row_ids[t_mine] : -1;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int r = __shfl_sync(0xffffffffu, rid, c);
+          if (r < 0) continue;
+          __nv_bfloat16* orow = out + (size_t)r * ld_out;
+          orow[f0] = __float2bfloat16_rn(v0[c]);
+          orow[f0 + 128] = __float2bfloat16_rn(v1[c]);
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---- workspace ------------------------------------------------------------------
+struct DenseWs {
+  unsigned char* flags;  // [M]
+  int* rows;             // [cap]
+  int* counters;         // [4]
+  __nv_bfloat16* xd;     // [cap_pad, D]
+  __nv_bfloat16* hd;     // [cap_pad, H]
+  size_t total;
+};
+
+size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+DenseWs dense_ws_layout(void* base, int64_t M, int64_t D, int64_t H, int64_t cap) {
+  const int64_t cap_pad = (cap + kDenseTok - 1) / kDenseTok * kDenseTok;
+  unsigned char* p = static_cast<unsigned char*>(base);
+  DenseWs w;
+  size_t off = 0;
+  w.flags = p + off;
+  off += align256((size_t)M);
+  w.rows = reinterpret_cast<int*>(p + off);
+  off += align256((size_t)cap * 4);
+  w.counters = reinterpret_cast<int*>(p + off);
+  off += 256;
+  w.xd = reinterpret_cast<__nv_bfloat16*>(p + off);
+  off += align256((size_t)cap_pad * D * 2);
+  w.hd = reinterpret_cast<__nv_bfloat16*>(p + off);
+  off += align256((size_t)cap_pad * H * 2);
+  w.total = off;
+  return w;
+}
+
+template <bool DUAL>
+int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void* b,
+                      int64_t b_rows, int64_t K, const float* bias, void* out, const int* row_ids,
+                      const int* n_rows_ptr, int64_t ld_out, int64_t cap, cudaStream_t stream) {
+  constexpr int STAGES = 4;
+  CUtensorMap map_a0, map_a1, map_b;
+  if (int rc = make_map(&map_a0, a0, a_rows, K, 128)) return rc;
+  if (int rc = make_map(&map_a1, a1, a_rows, K, 128)) return rc;
+  if (int rc = make_map(&map_b, b, b_rows, K, kDenseTok)) return rc;
+  const size_t smem = (size_t)STAGES * (2 * kATileBytes + kDenseTok * 128) + 1024;
+  auto kern = dense_rows_gemm_kernel<kDenseTok, STAGES, DUAL>;
+  static size_t granted[64] = {0};
+  if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_gated_t2d_hybrid")) return rc;
+  dim3 grid((unsigned)(a_rows / (DUAL ? 128 : 256)), (unsigned)((cap + kDenseTok - 1) / kDenseTok), 1);
+  kern<<<grid, kThreadsTc, smem, stream>>>(map_a0, map_a1, map_b, bias,
+                                           static_cast<__nv_bfloat16*>(out), row_ids, n_rows_ptr,
+                                           (int)K, (int)ld_out);
+  return check_launch("b200_twell_gated_t2d_hybrid (dense rows)");
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+size_t b200_twell_hybrid_workspace_bytes(int64_t M, int64_t D, int64_t H, int64_t dense_cap) {
+  if (M <= 0 || D <= 0 || H <= 0 || dense_cap <= 0) return 0;
+  return dense_ws_layout(nullptr, M, D, H, dense_cap).total;
+}
+
+int b200_twell_gated_t2d_hybrid(const void* x, const void* packed, const void* gate,
+                                const float* gate_bias, const void* up, const void* down,
+                                const void* down_t, void* out, int64_t M, int64_t D, int64_t H,
+                                int cf, uint32_t flags, int64_t nnz_threshold, int64_t dense_cap,
+                                void* hybrid_ws, size_t hybrid_ws_bytes, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+  const char* fn = "b200_twell_gated_t2d_hybrid";
+  if (int rc = check_dims(fn, M, D, H, cf)) return rc;
+  if (flags & ~B200_FLAG_HIGH_PRECISION) return fail(B200_EINVAL, "%s: unknown flags 0x%x", fn, flags);
+  if (dense_cap <= 0 || nnz_threshold < 0)
+    return fail(B200_EINVAL, "%s: need dense_cap > 0 and nnz_threshold >= 0", fn);
+  if (M == 0) return B200_OK;
+  if (M > (int64_t)1 << 20) return fail(B200_EUNSUPPORTED, "%s: M > 2^20 rows", fn);
+  if (dense_cap > M) dense_cap = M;
+  const void* ptrs[8] = {x, packed, gate, up, down, down_t, out, hybrid_ws};
+  const char* names[8] = {"x", "packed", "gate", "up", "down", "down_t", "out", "hybrid_ws"};
+  for (int i = 0; i < 8; ++i) {
+    if (ptrs[i] == nullptr) return fail(B200_ENULL, "%s: %s is NULL", fn, names[i]);
+    if (!aligned16(ptrs[i])) return fail(B200_EALIGN, "%s: %s is not 16-byte aligned", fn, names[i]);
+  }
+  if (reinterpret_cast<uintptr_t>(hybrid_ws) & 255u)
+    return fail(B200_EALIGN, "%s: hybrid_ws is not 256-byte aligned", fn);
+  DenseWs w = dense_ws_layout(hybrid_ws, M, D, H, dense_cap);
+  if (hybrid_ws_bytes < w.total)
+    return fail(B200_EWORKSPACE, "%s: hybrid_ws holds %zu bytes, %zu needed", fn, hybrid_ws_bytes,
+                w.total);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int tiles = (int)(H / kTileN), slab_w = kTileN / cf;
+  const int64_t cap_pad = (dense_cap + kDenseTok - 1) / kDenseTok * kDenseTok;
+
+  route_flags_kernel<<<(unsigned)((M + 7) / 8), 256, 0, st>>>(
+      static_cast<const uint32_t*>(packed), (int)M, tiles, slab_w,
+      (int)(nnz_threshold > 0x7fffffff ? 0x7fffffff : nnz_threshold), w.flags);
+  route_compact_kernel<<<1, 1024, 0, st>>>(w.flags, (int)M, (int)dense_cap, w.rows, w.counters);
+  if (int rc = check_launch(fn)) return rc;
+  if (int rc = twell_t2d_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, packed, up, down,
+                                out, M, D, H, cf, workspace, workspace_bytes, sm_count(), st,
+                                w.flags))
+    return rc;
+  gather_rows_kernel<<<(unsigned)dense_cap, 256, 0, st>>>(
+      static_cast<const uint4*>(x), w.rows, w.counters, reinterpret_cast<uint4*>(w.xd),
+      (int)(D / 8));
+  if (int rc = check_launch(fn)) return rc;
+  if (int rc = launch_dense_gemm<true>(gate, up, H, w.xd, cap_pad, D, gate_bias, w.hd, nullptr,
+                                       w.counters, H, dense_cap, st))
+    return rc;
+  return launch_dense_gemm<false>(down_t, down_t, D, w.hd, cap_pad, H, nullptr, out, w.rows,
+                                  w.counters, D, dense_cap, st);
+}
+
+int b200_twell_gated_mlp_hybrid(const void* x, const void* gate, const float* gate_bias,
+                                const void* up, const void* down, const void* down_t,
+                                void* packed, void* out, int64_t M, int64_t D, int64_t H, int cf,
+                                uint32_t flags, int64_t nnz_threshold, int64_t dense_cap,
+                                void* hybrid_ws, size_t hybrid_ws_bytes, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+  if (int rc = b200_twell_pack(x, gate, gate_bias, packed, M, D, H, cf, stream)) return rc;
+  return b200_twell_gated_t2d_hybrid(x, packed, gate, gate_bias, up, down, down_t, out, M, D, H,
+                                     cf, flags, nnz_threshold, dense_cap, hybrid_ws,
+                                     hybrid_ws_bytes, workspace, workspace_bytes, stream);
+}
+
+/* counters_out[0] = rows routed to the dense path by the last call on this workspace,
+ * [1] = overflowed rows left on the sparse path (capacity exhausted), [2] = rows that
+ * qualified.  Synchronises the device. */
+int b200_twell_hybrid_counters(const void* hybrid_ws, int64_t M, int64_t D, int64_t H,
+                               int64_t dense_cap, int* counters_out) {
+  if (hybrid_ws == nullptr || counters_out == nullptr || M <= 0 || dense_cap <= 0) return B200_EINVAL;
+  if (dense_cap > M) dense_cap = M;
+  DenseWs w = dense_ws_layout(const_cast<void*>(hybrid_ws), M, D, H, dense_cap);
+  if (cudaMemcpy(counters_out, w.counters, 3 * sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return fail(B200_ECUDA, "b200_twell_hybrid_counters: copy failed");
+  return B200_OK;
+}
+
+/* Error word raised by a bounded wait that gave up in the dense GEMMs (0 = none).  Reads and
+ * clears it; synchronises the device. */
+int b200_twell_hybrid_status(void) {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_dense_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_dense_error, &zero, sizeof(int));
+  return v;
+}
+
+}  // extern "C"

@@ -55,7 +55,8 @@ __global__ void __launch_bounds__(NI * 32)
 twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
                  const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
                  __nv_bfloat16* out, int M, int tiles, int slab_w, int cs, int nc,
-                 float* ws_partial, unsigned int* ws_counter) {
+                 float* ws_partial, unsigned int* ws_counter,
+                 const unsigned char* __restrict__ skip_rows) {
   constexpr int D = NI * 256;
   constexpr int NTHREADS = NI * 32;
   __shared__ int tile_off[kMaxTiles + 1];
@@ -70,6 +71,9 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
   const int crank = blockIdx.x % cs;
   const int cidx = (blockIdx.x / cs) % nc;
   const int row = blockIdx.x / (cs * nc);
+  // Rows routed to the dense tensor-core path: every CTA of every cluster of the row leaves
+  // (the row is uniform per cluster, so no cluster barrier is left half-attended).
+  if (skip_rows != nullptr && skip_rows[row]) return;
   const uint32_t* prow = packed + (size_t)row * tiles * slab_w;
   // Remote shared memory may only be touched once every CTA of the cluster runs:
   // arrive now, wait right before the first remote store.
@@ -290,7 +294,7 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
 template <int NI, bool GATED, bool HP>
 int launch_t2d(const void* x, const void* packed, const void* up, const void* down, void* out,
                int64_t M, int64_t H, int cf, int cs, int nc, float* ws_partial,
-               unsigned int* ws_counter, cudaStream_t stream) {
+               unsigned int* ws_counter, const unsigned char* skip_rows, cudaStream_t stream) {
   const int slab_w = kTileN / cf;
   const int tiles = (int)(H / kTileN);
   auto kern = twell_t2d_kernel<NI, GATED, HP>;
@@ -310,7 +314,7 @@ int launch_t2d(const void* x, const void* packed, const void* up, const void* do
       &cfg, kern, reinterpret_cast<const __nv_bfloat16*>(x),
       reinterpret_cast<const uint32_t*>(packed), reinterpret_cast<const __nv_bfloat16*>(up),
       reinterpret_cast<const __nv_bfloat16*>(down), reinterpret_cast<__nv_bfloat16*>(out), (int)M,
-      tiles, slab_w, cs, nc, ws_partial, ws_counter);
+      tiles, slab_w, cs, nc, ws_partial, ws_counter, skip_rows);
   if (e != cudaSuccess) return fail(B200_ECUDA, "twell_t2d: launch: %s", cudaGetErrorString(e));
   return B200_OK;
 }
@@ -318,12 +322,12 @@ int launch_t2d(const void* x, const void* packed, const void* up, const void* do
 template <bool GATED, bool HP>
 int dispatch_ni(int ni, const void* x, const void* packed, const void* up, const void* down,
                 void* out, int64_t M, int64_t H, int cf, int cs, int nc, float* ws_partial,
-                unsigned int* ws_counter, cudaStream_t stream) {
+                unsigned int* ws_counter, const unsigned char* skip_rows, cudaStream_t stream) {
   switch (ni) {
 #define B200_CASE(N)                                                                           \
   case N:                                                                                      \
     return launch_t2d<N, GATED, HP>(x, packed, up, down, out, M, H, cf, cs, nc, ws_partial,   \
-                                    ws_counter, stream);
+                                    ws_counter, skip_rows, stream);
     B200_CASE(1) B200_CASE(2) B200_CASE(3) B200_CASE(4) B200_CASE(5) B200_CASE(6) B200_CASE(7)
     B200_CASE(8) B200_CASE(9) B200_CASE(10) B200_CASE(11) B200_CASE(12) B200_CASE(13)
     B200_CASE(14) B200_CASE(15) B200_CASE(16)
@@ -360,7 +364,8 @@ void t2d_shape(int64_t M, int64_t D, int sm_count, size_t workspace_bytes, int* 
 
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
-                     void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+                     void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream,
+                     const unsigned char* skip_rows = nullptr) {
   int cs = 1, nc = 1;
   t2d_shape(M, D, sm_count, workspace != nullptr ? workspace_bytes : 0, &cs, &nc);
   unsigned int* counters = reinterpret_cast<unsigned int*>(workspace);
@@ -368,14 +373,14 @@ int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, con
   const int ni = (int)(D / 256);
   if (gated) {
     return hp ? dispatch_ni<true, true>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                        counters, stream)
+                                        counters, skip_rows, stream)
               : dispatch_ni<true, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                         counters, stream);
+                                         counters, skip_rows, stream);
   }
   return hp ? dispatch_ni<false, true>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                       counters, stream)
+                                       counters, skip_rows, stream)
             : dispatch_ni<false, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                        counters, stream);
+                                        counters, skip_rows, stream);
 }
 
 int sm_count();  // c_api.cu

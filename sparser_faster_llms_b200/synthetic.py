@@ -70,6 +70,36 @@ def make_tokens(m: int, d_model: int, *, seed: int = 1, fold_bias: bool = True,
     return x.to(dtype).to(device)
 
 
+def make_tokens_mixed_density(m: int, d_model: int, *, base_density: float, seed: int = 1,
+                              beta: tuple[float, float] = (2.0, 60.0),
+                              dense_fraction: float = 0.05,
+                              dense_range: tuple[float, float] = (0.2, 0.4),
+                              dtype: torch.dtype = torch.bfloat16, device="cpu"):
+    """Tokens whose gate density differs per token (prefill-like mix): most tokens draw their
+    density from ``Beta(*beta)``, a ``dense_fraction`` of them from ``U(*dense_range)``.
+
+    Works with a bias-folded FFN built for ``base_density`` (uniform neuron rates): the
+    per-neuron shift lives in ``gate[:, 0]`` and is multiplied by token feature 0, so feature 0
+    of token t is set to ``q(rho_t) / q(base_density)`` with ``q`` the Gaussian upper quantile.
+    Returns ``(x, rho)`` with ``rho`` the target density per token (fp32, CPU).
+    """
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, d_model, generator=gen)
+    a = torch.distributions.Gamma(torch.tensor(beta[0]), torch.tensor(1.0))
+    b = torch.distributions.Gamma(torch.tensor(beta[1]), torch.tensor(1.0))
+    torch.manual_seed(seed + 7919)  # the Gamma sampler has no generator argument
+    ga, gb = a.sample((m,)), b.sample((m,))
+    rho = (ga / (ga + gb)).double()
+    dense = torch.rand(m, generator=gen) < dense_fraction
+    lo, hi = dense_range
+    rho = torch.where(dense, lo + (hi - lo) * torch.rand(m, generator=gen).double(), rho)
+    rho = rho.clamp(1e-4, 0.49)
+    q = torch.special.ndtri(1.0 - rho) / torch.special.ndtri(torch.tensor(1.0 - base_density,
+                                                                          dtype=torch.float64))
+    x[:, 0] = q.float()
+    return x.to(dtype).to(device), rho.float()
+
+
 def dyadic_case(m: int, d_model: int, d_ff: int, *, seed: int = 0, device="cpu"):
     """Inputs on a coarse dyadic grid: every fp32 partial sum of x.w is exact.
 

@@ -21,6 +21,7 @@ pybind extension.  Differences a caller can observe:
 from __future__ import annotations
 
 import abc
+import ctypes
 import os
 from pathlib import Path
 from types import SimpleNamespace
@@ -438,10 +439,82 @@ def _gated_mlp(layer_number, A, UP, DOWN, C_packed, OUT, highest_precision, cf) 
     _check_packed(C_packed, m, h, cf, "C_packed")
     dev = _same_device(A, GATE, UP, DOWN, C_packed, OUT)
     flags = _lib.FLAG_HIGH_PRECISION if highest_precision else 0
-    _lib.call("b200_twell_gated_mlp", dev, A.data_ptr(), GATE.data_ptr(),
-              _lib.ptr(entry["bias"]), UP.data_ptr(), DOWN.data_ptr(), C_packed.data_ptr(),
-              OUT.data_ptr(), m, d, h, cf, flags, *_lib.workspace(dev))
+    route = entry.get("dense_route")
+    if route is not None and m >= route["min_tokens"]:
+        cap = route["dense_cap"]
+        cap = min(m, (max(128, m // 4) + 127) // 128 * 128) if cap is None else min(m, int(cap))
+        thr = route["nnz_threshold"]
+        thr = h // 16 if thr is None else int(thr)
+        ws_ptr, ws_bytes = _hybrid_workspace(dev, m, d, h, cap)
+        _lib.call("b200_twell_gated_mlp_hybrid", dev, A.data_ptr(), GATE.data_ptr(),
+                  _lib.ptr(entry["bias"]), UP.data_ptr(), DOWN.data_ptr(),
+                  route["DOWN_T"].data_ptr(), C_packed.data_ptr(), OUT.data_ptr(), m, d, h, cf,
+                  flags, thr, cap, ws_ptr, ws_bytes, *_lib.workspace(dev))
+        route["last"] = (m, d, h, cap)
+    else:
+        _lib.call("b200_twell_gated_mlp", dev, A.data_ptr(), GATE.data_ptr(),
+                  _lib.ptr(entry["bias"]), UP.data_ptr(), DOWN.data_ptr(), C_packed.data_ptr(),
+                  OUT.data_ptr(), m, d, h, cf, flags, *_lib.workspace(dev))
     entry["m"] = m
+
+
+# One growing scratch buffer per device for the dense-row route (calls on a stream are
+# serialised, so all layers share it).
+_HYBRID_WS: dict[int, torch.Tensor] = {}
+
+
+def _hybrid_workspace(dev: torch.device, m: int, d: int, h: int, cap: int) -> tuple[int, int]:
+    need = int(_lib.load_library().b200_twell_hybrid_workspace_bytes(m, d, h, cap))
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    buf = _HYBRID_WS.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.empty(need, dtype=torch.uint8, device=dev)
+        _HYBRID_WS[key] = buf
+    return buf.data_ptr(), buf.numel()
+
+
+def set_d2t_layer_dense_route(layer_number: int, DOWN_T: torch.Tensor | None, *,
+                              dense_cap: int | None = None, nnz_threshold: int | None = None,
+                              min_tokens: int = 256) -> None:
+    """Extension: route dense-enough token rows of one cached gated layer to tensor-core GEMMs.
+
+    ``DOWN_T`` is ``down_proj.weight`` itself, ``[D, H]`` bf16 contiguous (``None`` switches the
+    route off = reference behaviour).  Rows with more than ``nnz_threshold`` gate positives
+    (default ``H // 16``) or with an overflowed slab tile are computed densely, at most
+    ``dense_cap`` of them per call (default a quarter of the rows); calls with fewer than
+    ``min_tokens`` rows keep the gather kernel for every row.  The reference's TwELL path
+    has no such route and drops overflowed entries; its hybrid format has the dense tail
+    (hybrid_sp.cu:516-576).
+    """
+    entry = _layer(layer_number)
+    if DOWN_T is None:
+        entry.pop("dense_route", None)
+        return
+    _need(DOWN_T, "DOWN_T", torch.bfloat16)
+    h, d = entry["B"].shape
+    if DOWN_T.shape != (d, h):
+        raise ValueError(f"DOWN_T must be [{d}, {h}], got {tuple(DOWN_T.shape)}")
+    entry["dense_route"] = {"DOWN_T": DOWN_T, "dense_cap": dense_cap,
+                            "nnz_threshold": nnz_threshold, "min_tokens": int(min_tokens),
+                            "last": None}
+
+
+def d2t_layer_dense_route_counters(layer_number: int) -> dict | None:
+    """``{"dense_rows", "lossy_rows_left_sparse", "qualified_rows"}`` of the last routed call
+    of this layer, or None if it has not run one.  Synchronises the device; valid only until
+    another layer's routed call reuses the shared scratch buffer."""
+    route = _layer(layer_number).get("dense_route")
+    if route is None or route["last"] is None:
+        return None
+    m, d, h, cap = route["last"]
+    dev = route["DOWN_T"].device
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    out = (ctypes.c_int * 3)()
+    with torch.cuda.device(dev):
+        _lib.check("b200_twell_hybrid_counters",
+                   _lib.load_library().b200_twell_hybrid_counters(
+                       _HYBRID_WS[key].data_ptr(), m, d, h, cap, out))
+    return {"dense_rows": out[0], "lossy_rows_left_sparse": out[1], "qualified_rows": out[2]}
 
 
 def _plain_mlp(layer_number, A, DOWN, C_packed, OUT, num_splits) -> None:
@@ -748,8 +821,12 @@ class _BaseTwELLMLP(nn.Module, abc.ABC):
                               compression_factor=self.compression_factor, ext=self.ext)
         if self._gate_bias is not None:
             set_d2t_layer_bias(self.layer_number, self._gate_bias)
+        self._apply_dense_route()
         self._runtime_forward = self._forward_impl
         return self._forward_impl(A)
+
+    def _apply_dense_route(self) -> None:  # gated modules override
+        pass
 
     def set_gate_bias(self, bias: torch.Tensor | None) -> None:
         """Extension: per-neuron bias added before the ReLU (None = reference behaviour)."""
@@ -857,11 +934,40 @@ class TwELLGatedMLP(_BaseTwELLMLP):
         self.register_buffer("GATE", gate)
         self.register_buffer("UP", up)
         self.register_buffer("DOWN", down)
+        self._dense_route: dict | None = None
+        self._down_t: torch.Tensor | None = None
         self._forward_impl = self._select_forward_impl()
         self._finalize_runtime_forward()
 
     def _get_d2t_weight(self) -> torch.Tensor:
         return self.GATE
+
+    def enable_dense_route(self, dense_cap: int | None = None, nnz_threshold: int | None = None,
+                           min_tokens: int = 256) -> None:
+        """Extension (off by default = reference behaviour): for calls with at least
+        ``min_tokens`` rows, compute dense-enough or overflowed token rows as tensor-core GEMMs
+        instead of per-entry gathers (see :func:`set_d2t_layer_dense_route`).  Keeps a
+        ``[D, H]`` copy of the down projection."""
+        self._dense_route = {"dense_cap": dense_cap, "nnz_threshold": nnz_threshold,
+                             "min_tokens": min_tokens}
+        if self.layer is not None:
+            self._apply_dense_route()
+
+    def disable_dense_route(self) -> None:
+        self._dense_route = None
+        self._down_t = None
+        if self.layer is not None:
+            set_d2t_layer_dense_route(self.layer_number, None)
+
+    def dense_route_counters(self) -> dict | None:
+        return d2t_layer_dense_route_counters(self.layer_number) if self.layer is not None else None
+
+    def _apply_dense_route(self) -> None:
+        if self._dense_route is None:
+            return
+        if self._down_t is None or self._down_t.device != self.DOWN.device:
+            self._down_t = self.DOWN.t().contiguous()
+        set_d2t_layer_dense_route(self.layer_number, self._down_t, **self._dense_route)
 
     def _select_forward_impl(self):
         if self.preallocate_shared_hidden_state:
