@@ -236,6 +236,18 @@ int b200_twell_gated_mlp_hybrid(const void* x, const void* gate, const float* ga
                                 void* hybrid_ws, size_t hybrid_ws_bytes, void* workspace,
                                 size_t workspace_bytes, void* stream);
 
+/*
+ * Every row on the dense route, with no slab, routing or gather: for token counts so
+ * large that the weights are amortised and the per-entry gather cannot win.
+ *   h_ws [M, H] bf16 = relu(x gate^T + gate_bias) * (x up^T)   (caller scratch)
+ *   out  [M, D] bf16 = h_ws . down,  down_t [D, H] bf16 as above.
+ * The function of SparseMLP's dense inference path (sparse_models.py:343-351) on
+ * tcgen05; the reference runs it through torch matmuls.
+ */
+int b200_dense_gated_mlp(const void* x, const void* gate, const float* gate_bias, const void* up,
+                         const void* down_t, void* h_ws, void* out, int64_t M, int64_t D,
+                         int64_t H, void* stream);
+
 /* counters_out[0] = rows the last call on this workspace routed to the dense path,
  * [1] = overflowed rows left on the sparse path because dense_cap was exhausted,
  * [2] = rows that qualified.  Synchronises the device. */

@@ -63,6 +63,7 @@ _PROTOTYPES = {
     "b200_twell_gated_mlp_hybrid": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int64, c_int,
                                             c_uint32, c_int64, c_int64, c_void_p, c_size_t,
                                             c_void_p, c_size_t, c_void_p]),
+    "b200_dense_gated_mlp": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int64, c_void_p]),
     "b200_twell_hybrid_counters": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64,
                                            ctypes.POINTER(c_int)]),
     "b200_twell_hybrid_status": (c_int, []),

@@ -47,6 +47,65 @@ def shard_weights(GATE: torch.Tensor, UP: torch.Tensor, DOWN: torch.Tensor, rank
     return g, UP[h0:h1].contiguous(), DOWN[h0:h1].contiguous()
 
 
+class _CopyToShards(torch.autograd.Function):
+    """Identity in forward (x is replicated); sums the ranks' input gradients in backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        acc = g.float() if g.dtype != torch.float32 else g.clone()
+        dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=ctx.group)
+        return acc.to(g.dtype), None
+
+
+class _ReduceFromShards(torch.autograd.Function):
+    """Sums the ranks' partial results in forward; the gradient passes through unchanged
+    (every rank holds the same upstream gradient of the replicated sum)."""
+
+    @staticmethod
+    def forward(ctx, y, group):
+        y = y.contiguous()
+        acc = y.float() if y.dtype != torch.float32 else y.clone()
+        dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=group)
+        return acc.to(y.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def sharded_ff_gated(X: torch.Tensor, G: torch.Tensor, K: torch.Tensor, V: torch.Tensor, *,
+                     process_group=None, local_op: Callable | None = None):
+    """Training forward of the hybrid operator over a d_ff shard; differentiable.
+
+    ``G/K/V`` are this rank's ``[H_local, D]`` rows (see :func:`shard_weights`), ``X [B,S,D]`` is
+    replicated.  Returns ``(out, l0, l1)`` equal on every rank: ``out`` and the two sparsity
+    statistics are sums over neurons, hence additive across shards (l0 = sum over neurons of
+    the firing rate, l1 = mean over tokens of sum |T|; custom_op.cpp:120-133), so the forward
+    needs one all-reduce of ``out`` and one of each scalar, the backward one all-reduce of
+    ``dX``; weight gradients stay shard-local.  ``local_op(X, G, K, V)`` returns at least
+    ``(out, l0, l1)`` and defaults to ``torch.ops.sparse_ops.ff_forward_gated``.  The
+    reference trains data-parallel only and has no counterpart.
+    """
+    if local_op is None:
+        from .sparse_ops import register_ops
+        register_ops()
+        local_op = torch.ops.sparse_ops.ff_forward_gated
+    single = not dist.is_initialized() or dist.get_world_size(process_group) == 1
+    Xs = X if single else _CopyToShards.apply(X, process_group)
+    out, l0, l1 = local_op(Xs, G, K, V)[:3]
+    if single:
+        return out, l0, l1
+    return (_ReduceFromShards.apply(out, process_group),
+            _ReduceFromShards.apply(l0, process_group),
+            _ReduceFromShards.apply(l1, process_group))
+
+
 class ShardedTwELLGatedMLP(nn.Module):
     """``TwELLGatedMLP`` over a d_ff shard plus the all-reduce of the FFN output.
 

@@ -440,7 +440,15 @@ def _gated_mlp(layer_number, A, UP, DOWN, C_packed, OUT, highest_precision, cf) 
     dev = _same_device(A, GATE, UP, DOWN, C_packed, OUT)
     flags = _lib.FLAG_HIGH_PRECISION if highest_precision else 0
     route = entry.get("dense_route")
-    if route is not None and m >= route["min_tokens"]:
+    if (route is not None and route["dense_all_tokens"] is not None
+            and m >= route["dense_all_tokens"]):
+        # so many tokens that every row is cheaper as dense GEMMs: no slab is produced
+        ws_ptr, _ = _hybrid_workspace(dev, m, d, h, 0)
+        _lib.call("b200_dense_gated_mlp", dev, A.data_ptr(), GATE.data_ptr(),
+                  _lib.ptr(entry["bias"]), UP.data_ptr(), route["DOWN_T"].data_ptr(), ws_ptr,
+                  OUT.data_ptr(), m, d, h)
+        route["last"] = None
+    elif route is not None and m >= route["min_tokens"]:
         cap = route["dense_cap"]
         cap = min(m, (max(128, m // 4) + 127) // 128 * 128) if cap is None else min(m, int(cap))
         thr = route["nnz_threshold"]
@@ -464,7 +472,10 @@ _HYBRID_WS: dict[int, torch.Tensor] = {}
 
 
 def _hybrid_workspace(dev: torch.device, m: int, d: int, h: int, cap: int) -> tuple[int, int]:
-    need = int(_lib.load_library().b200_twell_hybrid_workspace_bytes(m, d, h, cap))
+    if cap > 0:
+        need = int(_lib.load_library().b200_twell_hybrid_workspace_bytes(m, d, h, cap))
+    else:  # all rows dense: only the [M, H] bf16 hidden state
+        need = m * h * 2
     key = dev.index if dev.index is not None else torch.cuda.current_device()
     buf = _HYBRID_WS.get(key)
     if buf is None or buf.numel() < need:
@@ -475,16 +486,18 @@ def _hybrid_workspace(dev: torch.device, m: int, d: int, h: int, cap: int) -> tu
 
 def set_d2t_layer_dense_route(layer_number: int, DOWN_T: torch.Tensor | None, *,
                               dense_cap: int | None = None, nnz_threshold: int | None = None,
-                              min_tokens: int = 256) -> None:
+                              min_tokens: int = 256,
+                              dense_all_tokens: int | None = None) -> None:
     """Extension: route dense-enough token rows of one cached gated layer to tensor-core GEMMs.
 
     ``DOWN_T`` is ``down_proj.weight`` itself, ``[D, H]`` bf16 contiguous (``None`` switches the
     route off = reference behaviour).  Rows with more than ``nnz_threshold`` gate positives
     (default ``H // 16``) or with an overflowed slab tile are computed densely, at most
     ``dense_cap`` of them per call (default a quarter of the rows); calls with fewer than
-    ``min_tokens`` rows keep the gather kernel for every row.  The reference's TwELL path
-    has no such route and drops overflowed entries; its hybrid format has the dense tail
-    (hybrid_sp.cu:516-576).
+    ``min_tokens`` rows keep the gather kernel for every row.  Calls with at least
+    ``dense_all_tokens`` rows (default: never) skip the slab altogether and run every row
+    through the dense GEMMs.  The reference's TwELL path has no such route and drops
+    overflowed entries; its hybrid format has the dense tail (hybrid_sp.cu:516-576).
     """
     entry = _layer(layer_number)
     if DOWN_T is None:
@@ -496,7 +509,7 @@ def set_d2t_layer_dense_route(layer_number: int, DOWN_T: torch.Tensor | None, *,
         raise ValueError(f"DOWN_T must be [{d}, {h}], got {tuple(DOWN_T.shape)}")
     entry["dense_route"] = {"DOWN_T": DOWN_T, "dense_cap": dense_cap,
                             "nnz_threshold": nnz_threshold, "min_tokens": int(min_tokens),
-                            "last": None}
+                            "dense_all_tokens": dense_all_tokens, "last": None}
 
 
 def d2t_layer_dense_route_counters(layer_number: int) -> dict | None:
@@ -943,13 +956,13 @@ class TwELLGatedMLP(_BaseTwELLMLP):
         return self.GATE
 
     def enable_dense_route(self, dense_cap: int | None = None, nnz_threshold: int | None = None,
-                           min_tokens: int = 256) -> None:
+                           min_tokens: int = 256, dense_all_tokens: int | None = None) -> None:
         """Extension (off by default = reference behaviour): for calls with at least
         ``min_tokens`` rows, compute dense-enough or overflowed token rows as tensor-core GEMMs
         instead of per-entry gathers (see :func:`set_d2t_layer_dense_route`).  Keeps a
         ``[D, H]`` copy of the down projection."""
         self._dense_route = {"dense_cap": dense_cap, "nnz_threshold": nnz_threshold,
-                             "min_tokens": min_tokens}
+                             "min_tokens": min_tokens, "dense_all_tokens": dense_all_tokens}
         if self.layer is not None:
             self._apply_dense_route()
 

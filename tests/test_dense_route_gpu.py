@@ -106,6 +106,28 @@ def test_small_calls_keep_the_gather_kernel():
     hybrid.destroy()
 
 
+@pytest.mark.parametrize("m", [200, 1024])
+def test_all_rows_dense_with_gate_bias(m):
+    """dense_all_tokens: no slab at all; also covers the explicit (not folded) gate bias and a
+    token count that is not a multiple of the 128-token tile."""
+    d, h = 1024, 4096
+    ffn = synthetic.make_ffn(d, h, seed=500 + m, density=0.05, fold_bias=False)
+    x = synthetic.make_tokens(m, d, seed=501, fold_bias=False)
+    ref = fo.dense_ffn(x, ffn.gate, ffn.up, ffn.down, gate_bias=ffn.gate_bias)
+    mod = twell.TwELLGatedMLP(7030, ffn.gate.to(DEV), ffn.up.to(DEV), ffn.down.to(DEV))
+    mod.set_gate_bias(ffn.gate_bias)
+    mod.enable_dense_route(dense_all_tokens=128)
+    y = mod(x.to(DEV))
+    torch.cuda.synchronize()
+    assert _lib.load_library().b200_twell_hybrid_status() == 0
+    assert row_rel_l2(y, ref).max() < REL_L2_ROW
+    # switching the route off returns to the slab path (reference behaviour)
+    mod.disable_dense_route()
+    y2 = mod(x.to(DEV))
+    assert row_rel_l2(y2, ref).max() < 3e-2
+    mod.destroy()
+
+
 def test_hybrid_entry_point_rejects_bad_arguments():
     lib = _lib.load_library()
     m, d, h = 256, 1024, 4096

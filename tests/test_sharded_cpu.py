@@ -97,6 +97,66 @@ def test_sharded_module_equals_unsharded(tmp_path, world, h):
     assert np.array_equal(tf.canonicalize(np.concatenate(parts, 1)), tf.canonicalize(full_packed))
 
 
+def _dense_training_op(X, G, K, V):
+    """Dense fp32 formula of the hybrid operator (out, l0, l1); autograd does the backward."""
+    m = X.shape[0] * X.shape[1]
+    g = torch.relu(X @ G.T)
+    t = g * (X @ K.T)
+    return t @ V, (g > 0).float().sum() / m, t.abs().sum() / m
+
+
+def _training_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        X, G, K, V, W = _training_case()
+        Gl, Kl, Vl = sharded.shard_weights(G, K, V, rank, world)
+        X = X.clone().requires_grad_(True)
+        Gl, Kl, Vl = (t.clone().requires_grad_(True) for t in (Gl, Kl, Vl))
+        out, l0, l1 = sharded.sharded_ff_gated(X, Gl, Kl, Vl, local_op=_dense_training_op)
+        loss = (out * W).sum() + 0.3 * l1
+        loss.backward()
+        h0, h1 = sharded.shard_range(G.shape[0], rank, world)
+        np.savez(os.path.join(out_dir, f"t{rank}.npz"), out=out.detach().numpy(),
+                 l0=l0.item(), l1=l1.item(), dX=X.grad.numpy(), dG=Gl.grad.numpy(),
+                 dK=Kl.grad.numpy(), dV=Vl.grad.numpy(), h0=h0, h1=h1)
+    finally:
+        dist.destroy_process_group()
+
+
+def _training_case():
+    gen = torch.Generator().manual_seed(123)
+    b, s, d, h = 2, 5, 64, 768
+    X = torch.randn(b, s, d, generator=gen)
+    G = torch.randn(h, d, generator=gen) * 0.1
+    K = torch.randn(h, d, generator=gen) * 0.1
+    V = torch.randn(h, d, generator=gen) * 0.1
+    W = torch.randn(b, s, d, generator=gen)
+    return X, G, K, V, W
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_training_forward_backward_equals_unsharded(tmp_path, world):
+    port = _free_port()
+    mp.spawn(_training_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    X, G, K, V, W = _training_case()
+    X.requires_grad_(True)
+    G.requires_grad_(True)
+    K.requires_grad_(True)
+    V.requires_grad_(True)
+    out, l0, l1 = _dense_training_op(X, G, K, V)
+    ((out * W).sum() + 0.3 * l1).backward()
+    outs = [np.load(tmp_path / f"t{r}.npz") for r in range(world)]
+    for o in outs:
+        assert np.allclose(o["out"], out.detach().numpy(), rtol=1e-4, atol=1e-5)
+        assert abs(o["l0"] - l0.item()) < 1e-3 and abs(o["l1"] - l1.item()) < 1e-4
+        assert np.allclose(o["dX"], X.grad.numpy(), rtol=1e-4, atol=1e-5)
+        h0, h1 = int(o["h0"]), int(o["h1"])
+        assert np.allclose(o["dG"], G.grad.numpy()[h0:h1], rtol=1e-4, atol=1e-5)
+        assert np.allclose(o["dK"], K.grad.numpy()[h0:h1], rtol=1e-4, atol=1e-5)
+        assert np.allclose(o["dV"], V.grad.numpy()[h0:h1], rtol=1e-4, atol=1e-5)
+
+
 def _early_exit_worker(rank, world, port):
     import datetime
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
