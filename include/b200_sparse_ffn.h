@@ -72,8 +72,10 @@ int b200_twell_pack(const void* x, const void* w, const float* bias, void* packe
  *   kernel 0 = automatic (M <= 16: split-k cluster kernel on mma.sync; 17..32: tcgen05
  *              split-k cluster kernel; M > 32: tcgen05 / TMEM / TMA tile kernel),
  *   kernel 1 = mma.sync split-k cluster kernel (any M),
- *   kernel 2 = tcgen05 tile kernel (64 or 128 tokens per CTA tile),
- *   kernel 3 = tcgen05 split-k cluster kernel (32 tokens per tile, D split 4 ways).
+ *   kernel 2 = tcgen05 tile kernel (64 or 128 tokens per CTA tile; from 1024 tokens on,
+ *              two co-resident 128-token CTAs per SM),
+ *   kernel 3 = tcgen05 split-k cluster kernel (32 tokens per tile, D split 4 ways),
+ *   kernel 4 = tcgen05 tile kernel, two co-resident 128-token CTAs per SM at any M.
  * All produce identical slab bytes on exact-arithmetic inputs.  No reference
  * counterpart (the reference has one WGMMA kernel, matmul_d2t.cu:287-709).
  */

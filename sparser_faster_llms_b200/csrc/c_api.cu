@@ -24,6 +24,8 @@ int twell_pack_tc(const void* x, const void* w, const float* bias, void* packed,
                   int64_t D, int64_t H, int cf, cudaStream_t stream);
 int twell_pack_tc_splitk(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                          int64_t D, int64_t H, int cf, cudaStream_t stream);
+int twell_pack_tc_pair(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                       int64_t D, int64_t H, int cf, cudaStream_t stream);
 int twell_pack_tc_status();
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
@@ -81,7 +83,7 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
                            int64_t M, int64_t D, int64_t H, int cf, int kernel, void* stream) {
   const char* fn = "b200_twell_pack";
   B200_TRY(check_dims(fn, M, D, H, cf));
-  if (kernel < 0 || kernel > 3) return fail(B200_EINVAL, "%s: kernel must be 0..3", fn);
+  if (kernel < 0 || kernel > 4) return fail(B200_EINVAL, "%s: kernel must be 0..4", fn);
   if (M == 0) return B200_OK;
   B200_TRY(check_ptr(fn, "x", x));
   B200_TRY(check_ptr(fn, "w", w));
@@ -97,6 +99,7 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
   // tcgen05 split-k kernel wins (12.5 vs 13.9 us).
   if (kernel == 3 || (kernel == 0 && M > 16 && M <= 32))
     return twell_pack_tc_splitk(x, w, bias, packed, M, D, H, cf, st);
+  if (kernel == 4) return twell_pack_tc_pair(x, w, bias, packed, M, D, H, cf, st);
   const bool use_tc = kernel == 2 || (kernel == 0 && M > 32);
   return use_tc ? twell_pack_tc(x, w, bias, packed, M, D, H, cf, st)
                 : twell_pack_small(x, w, bias, packed, M, D, H, cf, st);

@@ -35,8 +35,8 @@ namespace {
 __device__ int g_tc_error = 0;
 
 // grid = (H / 256, ceil(M / NTOK)).  Dynamic shared memory: STAGES x (A0 | A1 | B), 1024-aligned.
-template <int NTOK, int STAGES>
-__global__ void __launch_bounds__(kThreadsTc, 1)
+template <int NTOK, int STAGES, int MINB>
+__global__ void __launch_bounds__(kThreadsTc, MINB)
 twell_pack_tc_kernel(const __grid_constant__ CUtensorMap tmap_w,
                      const __grid_constant__ CUtensorMap tmap_x, const float* __restrict__ bias,
                      uint32_t* __restrict__ packed, int M, int D, int slab_w, int row_words) {
@@ -388,14 +388,14 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
 }
 
 // ---- host side -------------------------------------------------------------
-template <int NTOK, int STAGES>
+template <int NTOK, int STAGES, int MINB = 1>
 int launch_tc(const void* x, const void* w, const float* bias, void* packed, int64_t M, int64_t D,
               int64_t H, int cf, cudaStream_t stream) {
   CUtensorMap map_w, map_x;
   if (int rc = make_map(&map_w, w, H, D, 128)) return rc;
   if (int rc = make_map(&map_x, x, M, D, NTOK)) return rc;
   const size_t smem = (size_t)STAGES * (2 * kATileBytes + NTOK * 128) + 1024;
-  auto kern = twell_pack_tc_kernel<NTOK, STAGES>;
+  auto kern = twell_pack_tc_kernel<NTOK, STAGES, MINB>;
   static size_t granted[64] = {0};
   if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_pack")) return rc;
   const int slab_w = kTileN / cf;
@@ -451,11 +451,20 @@ int twell_pack_tc_splitk(const void* x, const void* w, const float* bias, void* 
 // Large-M path.  Needs D % 64 == 0 (guaranteed by D % 256 == 0).
 int twell_pack_tc(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                   int64_t D, int64_t H, int cf, cudaStream_t stream) {
-  // 256-token tiles raise the flops per byte staged through shared memory (the 128-token
-  // tile is bound by L2 -> SM bandwidth); they use all 512 TMEM columns.
-  if (M >= 1024) return launch_tc<256, 3>(x, w, bias, packed, M, D, H, cf, stream);
+  // From 1024 tokens on, two co-resident 128-token CTAs per SM (each 256 TMEM columns and two
+  // 48 KB stages) hide one CTA's pack epilogue under the other's MMAs.  Measured on B200,
+  // M = 16384, D = 2048, H = 8192: 991 TFLOP/s, against 758 for one 256-token CTA with three
+  // stages (cuBLAS matmul + relu: 1270); equal at D = 4096; no gain at M = 512.
+  if (M >= 1024) return launch_tc<128, 2, 2>(x, w, bias, packed, M, D, H, cf, stream);
   if (M > 64) return launch_tc<128, 4>(x, w, bias, packed, M, D, H, cf, stream);
   return launch_tc<64, 4>(x, w, bias, packed, M, D, H, cf, stream);
+}
+
+// Two co-resident CTAs of 128 tokens per SM (2 x 256 TMEM columns, 2 x 2 stages): one CTA's
+// pack epilogue runs under the other's MMAs.
+int twell_pack_tc_pair(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                       int64_t D, int64_t H, int cf, cudaStream_t stream) {
+  return launch_tc<128, 2, 2>(x, w, bias, packed, M, D, H, cf, stream);
 }
 
 // Error word raised by a bounded wait that gave up (0 = none).  Reads and clears it;
