@@ -75,7 +75,9 @@ int b200_twell_pack(const void* x, const void* w, const float* bias, void* packe
  *   kernel 2 = tcgen05 tile kernel (64 or 128 tokens per CTA tile; from 1024 tokens on,
  *              two co-resident 128-token CTAs per SM),
  *   kernel 3 = tcgen05 split-k cluster kernel (32 tokens per tile, D split 4 ways),
- *   kernel 4 = tcgen05 tile kernel, two co-resident 128-token CTAs per SM at any M.
+ *   kernel 4 = tcgen05 tile kernel, two co-resident 128-token CTAs per SM at any M,
+ *   kernel 5 = tcgen05 split-k cluster kernel with D split 8 ways (D % 512 == 0; chosen
+ *              automatically for 17..32 tokens when H <= 2048, e.g. a narrow d_ff shard).
  * All produce identical slab bytes on exact-arithmetic inputs.  No reference
  * counterpart (the reference has one WGMMA kernel, matmul_d2t.cu:287-709).
  */

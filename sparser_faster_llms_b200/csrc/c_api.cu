@@ -26,6 +26,8 @@ int twell_pack_tc_splitk(const void* x, const void* w, const float* bias, void* 
                          int64_t D, int64_t H, int cf, cudaStream_t stream);
 int twell_pack_tc_pair(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                        int64_t D, int64_t H, int cf, cudaStream_t stream);
+int twell_pack_tc_splitk8(const void* x, const void* w, const float* bias, void* packed,
+                          int64_t M, int64_t D, int64_t H, int cf, cudaStream_t stream);
 int twell_pack_tc_status();
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
@@ -83,7 +85,7 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
                            int64_t M, int64_t D, int64_t H, int cf, int kernel, void* stream) {
   const char* fn = "b200_twell_pack";
   B200_TRY(check_dims(fn, M, D, H, cf));
-  if (kernel < 0 || kernel > 4) return fail(B200_EINVAL, "%s: kernel must be 0..4", fn);
+  if (kernel < 0 || kernel > 5) return fail(B200_EINVAL, "%s: kernel must be 0..5", fn);
   if (M == 0) return B200_OK;
   B200_TRY(check_ptr(fn, "x", x));
   B200_TRY(check_ptr(fn, "w", w));
@@ -97,9 +99,15 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
   // Measured on B200 (D 2048, H 8192): up to 16 tokens the mma.sync cluster kernel is
   // fastest (9.6-9.9 us vs 11.7-12.4); at 17..32 tokens its mma work per CTA grows and the
   // tcgen05 split-k kernel wins (12.5 vs 13.9 us).
+  // A d_ff shard of at most 8 tiles (2048 neurons) fills too few SMs with a 4-way split:
+  // the 8-way split takes 8.5 us against 11.0 us there, but loses from 16 tiles on
+  // (15.9 against 11.2 us at 4096 neurons), where its 8-CTA clusters no longer fit one wave.
+  if (kernel == 0 && M > 16 && M <= 32 && H <= 8 * kTileN && D % 512 == 0)
+    return twell_pack_tc_splitk8(x, w, bias, packed, M, D, H, cf, st);
   if (kernel == 3 || (kernel == 0 && M > 16 && M <= 32))
     return twell_pack_tc_splitk(x, w, bias, packed, M, D, H, cf, st);
   if (kernel == 4) return twell_pack_tc_pair(x, w, bias, packed, M, D, H, cf, st);
+  if (kernel == 5) return twell_pack_tc_splitk8(x, w, bias, packed, M, D, H, cf, st);
   const bool use_tc = kernel == 2 || (kernel == 0 && M > 32);
   return use_tc ? twell_pack_tc(x, w, bias, packed, M, D, H, cf, st)
                 : twell_pack_small(x, w, bias, packed, M, D, H, cf, st);

@@ -448,6 +448,14 @@ int twell_pack_tc_splitk(const void* x, const void* w, const float* bias, void* 
   return launch_tc_splitk<4, 5>(x, w, bias, packed, M, D, H, cf, stream);
 }
 
+// The same with D split 8 ways: twice the CTAs for narrow d_ff (a d_ff shard of 2048..4096
+// neurons has only 8..16 tiles).  Needs D % 512 == 0.
+int twell_pack_tc_splitk8(const void* x, const void* w, const float* bias, void* packed,
+                          int64_t M, int64_t D, int64_t H, int cf, cudaStream_t stream) {
+  if (D % 512) return fail(B200_EUNSUPPORTED, "b200_twell_pack: 8-way split needs D %% 512 == 0");
+  return launch_tc_splitk<8, 4>(x, w, bias, packed, M, D, H, cf, stream);
+}
+
 // Large-M path.  Needs D % 64 == 0 (guaranteed by D % 256 == 0).
 int twell_pack_tc(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                   int64_t D, int64_t H, int cf, cudaStream_t stream) {

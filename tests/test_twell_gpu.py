@@ -356,10 +356,16 @@ def test_tcgen05_pack_kernel_bit_exact_with_oracle_and_with_cluster_kernel(m, d,
     assert _lib.load_library().b200_twell_pack_tc_status() == 0
     got_cl = to_np_u32(_pack_with(1, xg, gg, cf))
     got_sk = to_np_u32(_pack_with(3, xg, gg, cf))
+    got_pair = to_np_u32(_pack_with(4, xg, gg, cf))  # two co-resident CTAs per SM
     assert _lib.load_library().b200_twell_pack_tc_status() == 0
     assert np.array_equal(got_tc, want)
     assert np.array_equal(got_cl, want)
     assert np.array_equal(got_sk, want)
+    assert np.array_equal(got_pair, want)
+    if d % 512 == 0:  # 8-way split of the reduction dimension
+        got_sk8 = to_np_u32(_pack_with(5, xg, gg, cf))
+        assert _lib.load_library().b200_twell_pack_tc_status() == 0
+        assert np.array_equal(got_sk8, want)
     assert tf.slab_counts(want, cf).sum() > 0
 
 
