@@ -1,7 +1,13 @@
 // extern "C" surface of the library: argument validation and dispatch.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
+
+// Built-in default of the programmatic-dependent-launch switch (B200_PDL overrides it).
+#ifndef B200_PDL_DEFAULT
+#define B200_PDL_DEFAULT 0
+#endif
 
 namespace b200 {
 
@@ -33,6 +39,15 @@ int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, con
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
                      void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream,
                      const unsigned char* skip_rows = nullptr);
+
+bool pdl_enabled() {
+  static int state = -1;
+  if (state < 0) {
+    const char* e = getenv("B200_PDL");
+    state = (e != nullptr) ? (e[0] != '0') : B200_PDL_DEFAULT;
+  }
+  return state != 0;
+}
 
 // Number of SMs of the current device (cached per device ordinal).
 int sm_count() {

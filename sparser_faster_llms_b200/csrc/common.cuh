@@ -57,6 +57,36 @@ inline int ensure_dynamic_smem(Kernel kern, size_t bytes, size_t (&granted)[64],
   return B200_OK;
 }
 
+// Programmatic dependent launch.  A kernel launched with the attribute below may become
+// resident while its predecessor in the stream still runs; it must execute pdl_wait() before
+// its first global read of data the predecessor may write and before its first global write
+// (the wait returns once the predecessor grid has completed and its memory is visible).
+// pdl_launch_dependents() lets the successor's CTAs be scheduled as soon as every CTA of
+// this grid has started.  Both are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Whether the decode kernels are launched with programmatic stream serialisation
+// (environment variable B200_PDL: "0" switches it off, anything else or unset keeps the
+// built-in default).
+bool pdl_enabled();
+
+// Per-thread switch for launches whose predecessor in the stream is not a kernel (a memset).
+inline bool& pdl_suppressed() {
+  static thread_local bool suppressed = false;
+  return suppressed;
+}
+
+// Appends the attribute to attrs[n] when enabled; returns the new count.
+inline unsigned add_pdl_attribute(cudaLaunchAttribute* attrs, unsigned n) {
+  if (!pdl_enabled() || pdl_suppressed()) return n;
+  attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[n].val.programmaticStreamSerializationAllowed = 1;
+  return n + 1;
+}
+
 __device__ __forceinline__ uint32_t bf16_bits(float v) {
   return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
 }

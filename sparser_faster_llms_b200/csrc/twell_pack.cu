@@ -81,6 +81,7 @@ twell_pack_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   const int tile = blockIdx.x / CL;
   const int m0 = blockIdx.y * TM;
   cluster.barrier_arrive();  // matched by barrier_wait() before the first remote store
+  pdl_wait();                // nothing is read or written before the predecessor has completed
 
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -164,6 +165,10 @@ twell_pack_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     }
   }
 
+  // The weight stream of this CTA is consumed: the next kernel's CTAs may take their places
+  // and wait, under this kernel's reduction and compaction.
+  pdl_launch_dependents();
+
   // Push the partial pre-activations to the CTA that finalises each token:
   // owner r receives rank q's values in part[(q*TOK + local token)][neuron].
   cluster.barrier_wait();  // every CTA of the cluster is running (arrived at kernel start)
@@ -242,13 +247,13 @@ int launch_pack(const void* x, const void* w, const float* bias, void* packed, i
   cfg.blockDim = dim3(WARPS * 32, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CL;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = add_pdl_attribute(attr, 1);
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, reinterpret_cast<const __nv_bfloat16*>(x),
                                      reinterpret_cast<const __nv_bfloat16*>(w), bias,
                                      reinterpret_cast<uint32_t*>(packed), (int)M, (int)D, slab_w,

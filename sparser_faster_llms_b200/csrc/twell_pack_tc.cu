@@ -261,6 +261,9 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_slot;
+  // Barriers, TMEM and the cluster hand-shake are set up; from here on the kernel reads x and
+  // writes the slab, so the predecessor in the stream must have completed.
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -279,6 +282,9 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
         tma_load_2d(st + kATileBytes, &tmap_w, kcoord, tile * kTileN + 128, &full_bar[s]);
         tma_load_2d(st + 2 * kATileBytes, &tmap_x, kcoord, m0, &full_bar[s]);
       }
+      // Every load of this CTA is in flight: the contraction's CTAs may now take their
+      // places and wait, under this kernel's epilogue.
+      pdl_launch_dependents();
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -424,13 +430,13 @@ int launch_tc_splitk(const void* x, const void* w, const float* bias, void* pack
   cfg.blockDim = dim3(kThreadsTc, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CL;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = add_pdl_attribute(attr, 1);
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, bias,
                                      static_cast<uint32_t*>(packed), (int)M, (int)D, slab_w,
                                      tiles * slab_w);

@@ -71,6 +71,8 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
   const int crank = blockIdx.x % cs;
   const int cidx = (blockIdx.x / cs) % nc;
   const int row = blockIdx.x / (cs * nc);
+  // Nothing of the predecessor's output (slab, routing flags) is read before it has completed.
+  pdl_wait();
   // Rows routed to the dense tensor-core path: every CTA of every cluster of the row leaves
   // (the row is uniform per cluster, so no cluster barrier is left half-attended).
   if (skip_rows != nullptr && skip_rows[row]) return;
@@ -231,6 +233,11 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
     __syncthreads();  // entries are rewritten by the next chunk
   }
 
+  // The row gather is over: let the next kernel of the stream take its places (and run its
+  // set-up) under this kernel's reduction tail.  Scheduling it earlier costs more than it
+  // gains: its resident CTAs shrink the L1 of the gather (measured: 0.79 vs 0.73 ms/step).
+  pdl_launch_dependents();
+
   // Push this CTA's column sums to the owners: CTA r owns columns [r*cols, (r+1)*cols)
   // and receives rank q's contribution in inbox[q*cols .. (q+1)*cols).
   const int cols = D / cs;
@@ -303,13 +310,13 @@ int launch_t2d(const void* x, const void* packed, const void* up, const void* do
   cfg.blockDim = dim3(NI * 32, 1, 1);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)cs;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = add_pdl_attribute(attr, 1);
   cudaError_t e = cudaLaunchKernelEx(
       &cfg, kern, reinterpret_cast<const __nv_bfloat16*>(x),
       reinterpret_cast<const uint32_t*>(packed), reinterpret_cast<const __nv_bfloat16*>(up),
@@ -471,7 +478,10 @@ extern "C" int b200_twell_gated_t2d_noalloc(const void* x, const void* packed, c
   cudaError_t e = cudaMemsetAsync(scratch, 0, b200::kCounterWords * sizeof(unsigned int), st);
   if (e != cudaSuccess)
     return b200::fail(B200_ECUDA, "%s: cudaMemsetAsync: %s", fn, cudaGetErrorString(e));
-  return b200::twell_t2d_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, packed, up, down,
-                                out, M, D, H, cf, scratch, kStaticScratchBytes, b200::sm_count(),
-                                st);
+  b200::pdl_suppressed() = true;  // the predecessor of this launch is the memset above
+  const int rc = b200::twell_t2d_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, packed,
+                                        up, down, out, M, D, H, cf, scratch, kStaticScratchBytes,
+                                        b200::sm_count(), st);
+  b200::pdl_suppressed() = false;
+  return rc;
 }

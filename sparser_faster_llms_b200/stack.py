@@ -26,7 +26,7 @@ class GraphedFFNStack:
     """
 
     def __init__(self, mlps, batch: int, *, return_last_only: bool = False,
-                 device: torch.device | str | None = None):
+                 device: torch.device | str | None = None, copy_chunk: int = 2):
         self.mlps = list(mlps)
         if not self.mlps:
             raise ValueError("need at least one module")
@@ -46,16 +46,35 @@ class GraphedFFNStack:
         out_shape = shape[1:] if self.return_last_only else shape
         self.y_host = torch.zeros(out_shape, dtype=torch.bfloat16).pin_memory()
         self.stream = torch.cuda.Stream(dev)
+        self.copy_stream = torch.cuda.Stream(dev)
+        self.copy_chunk = max(1, int(copy_chunk))
         self.graph: torch.cuda.CUDAGraph | None = None
         self._capture()
 
     def _body(self) -> None:
-        self.x_dev.copy_(self.x_host, non_blocking=True)
+        # The host -> device copies run on a second stream in chunks of a few layers, each
+        # chunk followed by an event the compute stream waits on: layer l starts as soon as
+        # its own input has arrived, and the rest of the transfer hides under the kernels.
+        main = torch.cuda.current_stream(self.device)
+        self.copy_stream.wait_stream(main)
+        ready = []
+        with torch.cuda.stream(self.copy_stream):
+            for l0 in range(0, self.layers, self.copy_chunk):
+                l1 = min(self.layers, l0 + self.copy_chunk)
+                self.x_dev[l0:l1].copy_(self.x_host[l0:l1], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.copy_stream)
+                ready.append(ev)
         for l, mlp in enumerate(self.mlps):
+            if l % self.copy_chunk == 0:
+                main.wait_event(ready[l // self.copy_chunk])
             y = mlp(self.x_dev[l])
-            if y.data_ptr() != self.y_dev[l].data_ptr():
+            # only what is returned is gathered: with return_last_only the last layer's
+            # output goes to the host straight from the module's own tensor
+            if not self.return_last_only and y.data_ptr() != self.y_dev[l].data_ptr():
                 self.y_dev[l].copy_(y)
-        src = self.y_dev[-1] if self.return_last_only else self.y_dev
+        main.wait_stream(self.copy_stream)
+        src = y.view(self.batch, self.d_model) if self.return_last_only else self.y_dev
         self.y_host.copy_(src, non_blocking=True)
 
     def _capture(self) -> None:
