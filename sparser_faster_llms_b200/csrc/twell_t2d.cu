@@ -41,8 +41,7 @@ constexpr int kChunk = 256;     // entries staged in shared memory at a time
 #ifndef B200_T2D_DEPTH
 #define B200_T2D_DEPTH 8
 #endif
-constexpr int kDepth = B200_T2D_DEPTH;  // entries per batch (row loads in flight per lane: 2x gated)
-constexpr int kStageWords = 4096;  // slab rows up to this many words are staged in shared memory
+constexpr int kDepth = B200_T2D_DEPTH;  // entries per batch (row loads in flight per lane: 2x gated)constexpr int kStageWords = 4096;  // slab rows up to this many words are staged in shared memory
 
 __device__ __forceinline__ uint4 ldg_nc(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
@@ -148,8 +147,8 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
     }
     __syncthreads();
 
-    for (int e0 = 0; e0 < n; e0 += kDepth, buf ^= 1) {
-      uint4 uv[GATED ? kDepth : 1], dv[kDepth];
+    // Row loads of a batch: kDepth entries, this lane's 16 bytes of the up and the down row.
+    auto fetch = [&](int e0, uint4 (&uv)[GATED ? kDepth : 1], uint4 (&dv)[kDepth]) {
 #pragma unroll
       for (int q = 0; q < kDepth; ++q) {
         if (e0 + q < n) {
@@ -161,6 +160,8 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
           dv[q] = make_uint4(0u, 0u, 0u, 0u);
         }
       }
+    };
+    auto consume = [&](int e0, uint4 (&uv)[GATED ? kDepth : 1], uint4 (&dv)[kDepth]) {
       if (GATED) {
         // pass A: this warp's slice of the kDepth dot products (independent chains)
         float u[kDepth];
@@ -229,6 +230,16 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
           }
         }
       }
+      buf ^= 1;
+    };
+    // One batch at a time.  Requesting batch b + 1 before batch b is reduced (two register
+    // buffers) was measured and does not pay: with 4 entries per buffer 13.97 vs 12.32 us per
+    // launch at batch 32, and 6 or 8 per buffer push the kernel past 128 registers and halve
+    // its occupancy (23.9 / 25.5 us).
+    for (int e0 = 0; e0 < n; e0 += kDepth) {
+      uint4 uv[GATED ? kDepth : 1], dv[kDepth];
+      fetch(e0, uv, dv);
+      consume(e0, uv, dv);
     }
     __syncthreads();  // entries are rewritten by the next chunk
   }
