@@ -173,10 +173,64 @@ def case_signatures(twell_ref, out: Path):
     (out / "twell_signatures.json").write_text(json.dumps(sigs, indent=1, sort_keys=True))
 
 
+def state_dict_inputs():
+    """Small seeded state dicts in the three layouts the reference converts between
+    (HF linears, raw parameters, TwELL buffers), gated and not, with auxiliary keys."""
+    gen = torch.Generator().manual_seed(2024)
+    d, h = 6, 10
+    r = lambda *s: torch.randn(*s, generator=gen)  # noqa: E731
+    gated_hf = {"model.embed.weight": r(7, d), "tracker.count": r(3),
+                "model.layers.0.mlp.metrics_accumulator.x": r(2)}
+    gated_raw, gated_twell, plain_raw = {"lm_head.weight": r(7, d)}, {"norm.weight": r(d)}, {}
+    for l in range(2):
+        p = f"model.layers.{l}.mlp."
+        gated_hf.update({p + "gate_proj.weight": r(h, d), p + "up_proj.weight": r(h, d),
+                         p + "down_proj.weight": r(d, h), p + "tracker.last": r(h)})
+        gated_raw.update({p + "gate_weight": r(d, h), p + "up_weight": r(h, d),
+                          p + "down_weight": r(h, d)})
+        gated_twell.update({p + "GATE": r(h, d), p + "UP": r(h, d), p + "DOWN": r(h, d)})
+        plain_raw.update({p + "up_weight": r(d, h), p + "down_weight": r(h, d)})
+    return {"gated_hf": (gated_hf, True), "gated_raw": (gated_raw, True),
+            "gated_twell": (gated_twell, True), "plain_raw": (plain_raw, False)}
+
+
+def case_state_dicts(reference_root: str, out: Path):
+    """Outputs of the reference's sparse_to_hf_state_dict / sparse_to_twell_state_dict
+    (custom_models/sparse_testing_utils.py:182-207): key -> [shape, sha256 of the bytes]."""
+    import importlib.util
+    import json
+    import types
+    # sparse_testing_utils imports the TwELL module classes only to build modules; give it
+    # the file-loaded reference twell module under the package name it expects.
+    spec = importlib.util.spec_from_file_location(
+        "custom_models.twell_modules.twell",
+        Path(reference_root) / "custom_models/twell_modules/twell.py")
+    tw = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(tw)
+    sys.modules.setdefault("custom_models.twell_modules", types.ModuleType("custom_models.twell_modules"))
+    sys.modules["custom_models.twell_modules.twell"] = tw
+    spec = importlib.util.spec_from_file_location(
+        "ref_sparse_testing_utils", Path(reference_root) / "custom_models/sparse_testing_utils.py")
+    stu = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(stu)
+    digest = lambda sd: {k: [list(v.shape), sha(v)] for k, v in sd.items()}  # noqa: E731
+    golden = {}
+    for name, (sd, gated) in state_dict_inputs().items():
+        golden[name] = {"hf": digest(stu.sparse_to_hf_state_dict(sd, gated=gated)),
+                        "twell": digest(stu.sparse_to_twell_state_dict(sd, gated=gated)),
+                        "hf_keep_aux": digest(stu.sparse_to_hf_state_dict(
+                            sd, drop_auxiliary=False, gated=gated))}
+    (out / "state_dict_conversions.json").write_text(json.dumps(golden, indent=1, sort_keys=True))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only-state-dicts", action="store_true")
     args = ap.parse_args()
+    if args.only_state_dicts:
+        case_state_dicts(args.reference, HERE)
+        return
     sys.path.insert(0, args.reference)
     from custom_models import sparse_models as ref
     import importlib.util
