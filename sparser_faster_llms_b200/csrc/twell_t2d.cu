@@ -41,7 +41,8 @@ constexpr int kChunk = 256;     // entries staged in shared memory at a time
 #ifndef B200_T2D_DEPTH
 #define B200_T2D_DEPTH 8
 #endif
-constexpr int kDepth = B200_T2D_DEPTH;  // entries per batch (row loads in flight per lane: 2x gated)constexpr int kStageWords = 4096;  // slab rows up to this many words are staged in shared memory
+constexpr int kDepth = B200_T2D_DEPTH;  // entries per batch (row loads in flight per lane: 2x gated)
+constexpr int kStageWords = 4096;  // slab rows up to this many words are staged in shared memory
 
 __device__ __forceinline__ uint4 ldg_nc(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
