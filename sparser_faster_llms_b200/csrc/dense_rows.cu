@@ -49,6 +49,10 @@ __device__ int g_dense_error = 0;
 #ifndef B200_DENSE_MINB
 #define B200_DENSE_MINB 2
 #endif
+// 1 / 0 force the persistent / the one-tile form of the GEMM; -1 chooses per call.
+#ifndef B200_DENSE_PERSISTENT
+#define B200_DENSE_PERSISTENT (-1)
+#endif
 constexpr int kDenseTok = B200_DENSE_TOK;
 constexpr int kDenseStages = B200_DENSE_STAGES;
 
@@ -291,6 +295,205 @@ dense_rows_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
   }
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent form of the same GEMM: one CTA per SM walks the (feature tile, token tile) list
+// with a stride of the grid, feature tile fastest, so the CTAs of a wave share one token tile.
+// TMEM holds two accumulator pairs (4 x NTOK columns): while the epilogue warps drain pair a
+// of tile i, the MMA thread already fills pair a^1 with tile i + 1, and the producer keeps
+// the shared-memory ring full across tile boundaries (one running stage counter).
+//   full / empty      : ring stages, as in the one-tile kernel;
+//   tfull[a]          : tcgen05.commit after the last k-step of a tile -> epilogue may read pair a;
+//   tempty[a]         : one epilogue thread arrives after all four warps have read pair a.
+// The grid is sized by the host for the capacity; the token-tile count comes from the
+// device-side row count, so no CTA is launched per empty tile.
+template <int NTOK, int STAGES, int NBUF, bool DUAL>
+__global__ void __launch_bounds__(kThreadsTc, NBUF == 1 ? 2 : 1)
+dense_rows_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_a0,
+                                  const __grid_constant__ CUtensorMap tmap_a1,
+                                  const __grid_constant__ CUtensorMap tmap_b,
+                                  const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                  const int* __restrict__ row_ids,
+                                  const int* __restrict__ n_rows_ptr, int n_rows_host, int K,
+                                  int ld_out, int feature_tiles) {
+  constexpr int kBTileBytes = NTOK * 128;
+  constexpr int kStageBytes = 2 * kATileBytes + kBTileBytes;
+  constexpr uint32_t kTmemCols = 2 * NTOK * NBUF;  // NBUF accumulator pairs
+  static_assert(kTmemCols <= 512, "TMEM has 512 columns");
+  constexpr uint32_t kIdesc = umma_idesc(128, NTOK);
+
+  const int n_rows = n_rows_ptr != nullptr ? *n_rows_ptr : n_rows_host;
+  const int token_tiles = (n_rows + NTOK - 1) / NTOK;
+  const int total = feature_tiles * token_tiles;
+  if ((int)blockIdx.x >= total) return;  // uniform for the CTA: nothing allocated yet
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], tfull_bar[2], tempty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ksteps = K / kStageK;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 1);
+    }
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer ----
+    if (lane == 0) {
+      uint32_t it = 0;  // ring position, running across tiles
+      for (int t = blockIdx.x; t < total && !abort_s; t += gridDim.x) {
+        const int ft = t % feature_tiles, m0 = (t / feature_tiles) * NTOK;
+        const int a0_row = DUAL ? ft * 128 : ft * 256;
+        const int a1_row = DUAL ? ft * 128 : ft * 256 + 128;
+        for (int k = 0; k < ksteps; ++k, ++it) {
+          const int s = (int)(it % STAGES);
+          const uint32_t phase = (it / STAGES) & 1u;
+          if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+            abort_s = 1;
+            atomicExch(&g_dense_error, 1);
+            break;
+          }
+          unsigned char* st = smem + (size_t)s * kStageBytes;
+          mbar_expect_tx(&full_bar[s], (uint32_t)kStageBytes);
+          tma_load_2d(st, &tmap_a0, k * kStageK, a0_row, &full_bar[s]);
+          tma_load_2d(st + kATileBytes, DUAL ? &tmap_a1 : &tmap_a0, k * kStageK, a1_row,
+                      &full_bar[s]);
+          tma_load_2d(st + 2 * kATileBytes, &tmap_b, k * kStageK, m0, &full_bar[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      uint32_t it = 0;
+      int i = 0;
+      for (int t = blockIdx.x; t < total && !abort_s; t += gridDim.x, ++i) {
+        const int a = i % NBUF;
+        const uint32_t use = (uint32_t)(i / NBUF);
+        if (!mbar_wait(&tempty_bar[a], (use & 1u) ^ 1u)) {  // epilogue has drained this pair
+          abort_s = 1;
+          atomicExch(&g_dense_error, 4);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc0 = tmem_base + (uint32_t)(a * 2 * NTOK);
+        for (int k = 0; k < ksteps; ++k, ++it) {
+          const int s = (int)(it % STAGES);
+          const uint32_t phase = (it / STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], phase)) {
+            abort_s = 1;
+            atomicExch(&g_dense_error, 2);
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes);
+          const uint64_t da0 = umma_desc(sa), da1 = umma_desc(sa + kATileBytes),
+                         db = umma_desc(sa + 2 * kATileBytes);
+#pragma unroll
+          for (int kk = 0; kk < kStageK / 16; ++kk) {
+            const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
+            umma_bf16(acc0, da0 + 2 * kk, db + 2 * kk, kIdesc, acc);
+            umma_bf16(acc0 + NTOK, da1 + 2 * kk, db + 2 * kk, kIdesc, acc);
+          }
+          umma_commit(&empty_bar[s]);
+        }
+        if (abort_s) break;
+        umma_commit(&tfull_bar[a]);  // both accumulators of this tile are complete
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5 own TMEM lane quarters 2, 3, 0, 1 ----
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    int i = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x, ++i) {
+      const int a = i % NBUF;
+      const uint32_t use = (uint32_t)(i / NBUF);
+      const int ft = t % feature_tiles, m0 = (t / feature_tiles) * NTOK;
+      bool ok = mbar_wait(&tfull_bar[a], use & 1u);
+      if (!ok) {
+        abort_s = 1;
+        atomicExch(&g_dense_error, 3);
+      }
+      if (!epi_barrier_and(ok)) break;  // the same decision in all 128 epilogue threads
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t lane_addr =
+          tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 2 * NTOK);
+      const int f0 = (DUAL ? ft * 128 : ft * 256) + q * 32 + lane;
+      const float b0 = (DUAL && bias != nullptr) ? bias[f0] : 0.f;
+      for (int tb = 0; tb < NTOK / 32; ++tb) {
+        if (m0 + tb * 32 >= n_rows) break;
+        float v0[32], v1[32];
+        tmem_ld32(lane_addr + (uint32_t)(tb * 32), v0);
+        tmem_ld32(lane_addr + (uint32_t)(NTOK + tb * 32), v1);
+        if (DUAL) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int tok = m0 + tb * 32 + c;
+            if (tok >= n_rows) break;
+            const float g = v0[c] + b0;
+            float h = 0.f;
+            if (g > 0.f)
+              h = __bfloat162float(__float2bfloat16_rn(g)) * __bfloat162float(__float2bfloat16_rn(v1[c]));
+            out[(size_t)tok * ld_out + f0] = __float2bfloat16_rn(h);
+          }
+        } else {
+          const int t_mine = m0 + tb * 32 + lane;
+          const int rid = t_mine < n_rows ? (row_ids != nullptr ? row_ids[t_mine] : t_mine) : -1;
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int r = __shfl_sync(0xffffffffu, rid, c);
+            if (r < 0) continue;
+            __nv_bfloat16* orow = out + (size_t)r * ld_out;
+            orow[f0] = __float2bfloat16_rn(v0[c]);
+            orow[f0 + 128] = __float2bfloat16_rn(v1[c]);
+          }
+        }
+      }
+      // all four warps have read the pair: hand it back to the MMA thread
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      epi_barrier();
+      if (et == 0) mbar_arrive(&tempty_bar[a]);
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
 // ---- workspace ------------------------------------------------------------------
 struct DenseWs {
   unsigned char* flags;  // [M]
@@ -322,16 +525,55 @@ DenseWs dense_ws_layout(void* base, int64_t M, int64_t D, int64_t H, int64_t cap
   return w;
 }
 
+// Persistent form: NBUF accumulator pairs per CTA; one CTA per SM with two pairs and a deep
+// ring, or two CTAs per SM with one pair and two stages each.
+template <int STAGES, int NBUF, bool DUAL>
+int launch_persistent(const CUtensorMap& map_a0, const CUtensorMap& map_a1, const CUtensorMap& map_b,
+                      const float* bias, void* out, const int* row_ids, const int* n_rows_ptr,
+                      int64_t cap, int64_t K, int64_t ld_out, int feature_tiles, int64_t tiles_max,
+                      cudaStream_t stream) {
+  const size_t smem = (size_t)STAGES * (2 * kATileBytes + kDenseTok * 128) + 1024;
+  auto kern = dense_rows_gemm_persistent_kernel<kDenseTok, STAGES, NBUF, DUAL>;
+  static size_t granted[64] = {0};
+  if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_gated_t2d_hybrid")) return rc;
+  const int64_t slots = (int64_t)sm_count() * (NBUF == 1 ? 2 : 1);
+  const int ctas = (int)(tiles_max < slots ? tiles_max : slots);
+  kern<<<ctas, kThreadsTc, smem, stream>>>(map_a0, map_a1, map_b, bias,
+                                           static_cast<__nv_bfloat16*>(out), row_ids, n_rows_ptr,
+                                           (int)cap, (int)K, (int)ld_out, feature_tiles);
+  return check_launch("b200_twell_gated_t2d_hybrid (dense rows, persistent)");
+}
+
 template <bool DUAL>
 int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void* b,
                       int64_t b_rows, int64_t K, const float* bias, void* out, const int* row_ids,
                       const int* n_rows_ptr, int64_t ld_out, int64_t cap, cudaStream_t stream) {
   // cap: rows the grid covers; without a device-side count (n_rows_ptr == NULL) all of them
-  constexpr int STAGES = kDenseStages;
   CUtensorMap map_a0, map_a1, map_b;
   if (int rc = make_map(&map_a0, a0, a_rows, K, 128)) return rc;
   if (int rc = make_map(&map_a1, a1, a_rows, K, 128)) return rc;
   if (int rc = make_map(&map_b, b, b_rows, K, kDenseTok)) return rc;
+  // Which form.  Measured on B200, all three products, TFLOP/s at (M, D, H) =
+  // (2048, 2048, 11008) / (16384, 2048, 11008) / (2048, 4096, 16384) / (16384, 4096, 16384):
+  //   one-tile CTAs, two per SM              858 / 1118 / 1148 / 1108
+  //   persistent, two accumulator pairs      921 / 1042 /  896 /  893   (one CTA per SM)
+  //   persistent, one pair, two CTAs per SM  852 / 1041 / 1127 / 1069
+  // All are bound by the L2 -> SM operand stream (about 64 GB/s per SM through TMA), and two
+  // CTAs per SM keep more loads in flight than one deep ring.  The one-tile form is used when
+  // the host knows the row count; when the count lives on the device (routing) the
+  // persistent two-CTA form is used, because it launches no CTA per empty tile.
+  const int feature_tiles = (int)(a_rows / (DUAL ? 128 : 256));
+  const int64_t tiles_max = (int64_t)feature_tiles * ((cap + kDenseTok - 1) / kDenseTok);
+  int form = B200_DENSE_PERSISTENT;  // 0 one-tile CTAs, 1 persistent x 2 accumulator pairs,
+                                     // 2 persistent x 1 pair, two CTAs per SM
+  if (form < 0) form = (n_rows_ptr != nullptr) ? 2 : 0;
+  if (form == 1)
+    return launch_persistent<4, 2, DUAL>(map_a0, map_a1, map_b, bias, out, row_ids, n_rows_ptr, cap,
+                                         K, ld_out, feature_tiles, tiles_max, stream);
+  if (form == 2)
+    return launch_persistent<2, 1, DUAL>(map_a0, map_a1, map_b, bias, out, row_ids, n_rows_ptr, cap,
+                                         K, ld_out, feature_tiles, tiles_max, stream);
+  constexpr int STAGES = kDenseStages;
   const size_t smem = (size_t)STAGES * (2 * kATileBytes + kDenseTok * 128) + 1024;
   auto kern = dense_rows_gemm_kernel<kDenseTok, STAGES, DUAL>;
   static size_t granted[64] = {0};

@@ -109,6 +109,20 @@ __device__ __forceinline__ void epi_barrier() {  // the 128 epilogue threads onl
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
+// Barrier of the 128 epilogue threads that also ANDs a flag over them, so that a decision
+// taken after a bounded wait (carry on / give up) is the same in every epilogue thread and
+// no thread is left alone at a later epi_barrier().
+__device__ __forceinline__ bool epi_barrier_and(bool v) {
+  uint32_t r;
+  asm volatile(
+      "{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\n"
+      "bar.red.and.pred p, 1, 128, q;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(r)
+      : "r"((uint32_t)v)
+      : "memory");
+  return r != 0;
+}
+
 // ---- host side -------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,

@@ -133,6 +133,7 @@ twell_pack_tc_kernel(const __grid_constant__ CUtensorMap tmap_w,
       abort_s = 1;
       atomicExch(&g_tc_error, 3);
     }
+    ok = epi_barrier_and(ok);  // the same decision in all 128 epilogue threads
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int n_lo = tile * kTileN + q * 32 + lane;  // neuron of accumulator 0; +128 for 1
     const float b_lo = bias != nullptr ? bias[n_lo] : 0.f;
