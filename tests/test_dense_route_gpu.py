@@ -71,6 +71,29 @@ def test_hybrid_rows_match_dense_formula(m, d, h):
     hybrid.destroy()
 
 
+def test_hybrid_with_wider_slabs_cf4():
+    """cf = 4: 63 entries per tile, so only rows above ~25 % in some tile overflow; routing reads
+    the capacity from the slab width."""
+    m, d, h, cf = 384, 1024, 4096, 4
+    ffn, x, rho, ref = make_case(m, d, h, seed=905)
+    xg = x.to(DEV)
+    args = [ffn.gate.to(DEV), ffn.up.to(DEV), ffn.down.to(DEV)]
+    kw = dict(compression_factor=cf, flex_kernels=True)
+    sparse = twell.TwELLGatedMLP(7040, *args, **kw)
+    hybrid = twell.TwELLGatedMLP(7041, *args, **kw)
+    hybrid.enable_dense_route(nnz_threshold=h // 8, dense_cap=m, min_tokens=128)
+    y_sparse, y_hybrid = sparse(xg), hybrid(xg)
+    torch.cuda.synchronize()
+    counts = slab_counts(xg, ffn.gate.to(DEV), cf=cf)
+    qualifies = (counts.sum(1) > h // 8) | (counts > 63).any(1)
+    assert qualifies.sum() >= 4
+    assert hybrid.dense_route_counters()["dense_rows"] == int(qualifies.sum())
+    assert row_rel_l2(y_hybrid, ref).max() < REL_L2_ROW
+    assert torch.equal(y_hybrid.cpu()[~qualifies], y_sparse.cpu()[~qualifies])
+    sparse.destroy()
+    hybrid.destroy()
+
+
 def test_dense_cap_exhausted_leaves_later_rows_on_gather_path():
     m, d, h = 512, 1024, 4096
     ffn, x, rho, ref = make_case(m, d, h, seed=411)
