@@ -225,7 +225,8 @@ def case_state_dicts(reference_root: str, out: Path):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=str(REPO.parent / "reference"),
+                    help="checkout of the reference (default: a sibling of this repository)")
     ap.add_argument("--only-state-dicts", action="store_true")
     args = ap.parse_args()
     if args.only_state_dicts:
