@@ -7,6 +7,7 @@ current CUDA stream.
 from __future__ import annotations
 
 import ctypes
+import warnings
 from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
@@ -139,6 +140,7 @@ def current_stream_handle(device: torch.device) -> int:
 
 
 _WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+_WARNED_CAPTURE = False
 
 
 def workspace(device: torch.device) -> tuple[int | None, int]:
@@ -151,6 +153,14 @@ def workspace(device: torch.device) -> tuple[int | None, int]:
     ws = _WORKSPACES.get(key)
     if ws is None:
         if torch.cuda.is_current_stream_capturing():
+            global _WARNED_CAPTURE
+            if not _WARNED_CAPTURE:
+                _WARNED_CAPTURE = True
+                warnings.warn(
+                    "sparser_faster_llms_b200: a contraction is being captured on a stream that "
+                    "has no workspace yet, so it runs without the few-token multi-cluster shape. "
+                    "Run the step once on the capture stream before capturing "
+                    "(torch.cuda.graph(g, stream=s) with the warm-up on s).", stacklevel=3)
             return None, 0
         nbytes = int(load_library().b200_workspace_bytes())
         ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
