@@ -198,6 +198,23 @@ int b200_hybrid_spmm_t(const void* vals0, const void* vals1, const int* col_star
                        void* stream);
 
 /*
+ * Weight-gradient product on the tensor cores: out[H, D] = vals^T . rows, with vals a
+ * slab-shaped sparse [M, H] operand (dR, dU or T) and rows a dense [M, D] bf16 matrix (X or
+ * the output gradient).  The reduction runs over all M tokens and the result is dense, so
+ * for training-sized M this is a GEMM: the slab is scattered into a zero-filled K-major
+ * [H, M] matrix, rows is transposed once (reuse_rows_t = 1 reuses the transposed copy left
+ * in ws by the previous call with the same rows) and a tcgen05 GEMM does the rest.  Same
+ * result as b200_hybrid_csc_build + b200_hybrid_spmm_t (fp32 accumulation, bf16 store;
+ * the summation order differs), which remain the path for small M.  Replaces
+ * sparse_dense_gemm_hybrid_dense on transposed operands (custom_op.cpp:261-269).
+ * ws: b200_hybrid_wgrad_workspace_bytes(M, D, H) bytes, 256-byte aligned.
+ */
+size_t b200_hybrid_wgrad_workspace_bytes(int64_t M, int64_t D, int64_t H);
+int b200_hybrid_wgrad_dense(const void* vals_slab, const void* rows, void* out, int64_t M,
+                            int64_t D, int64_t H, int cf, int reuse_rows_t, void* ws,
+                            size_t ws_bytes, void* stream);
+
+/*
  * Row-ELL x dense: C[r,:] = sum_k vals[r,k] * B[cols[r,k],:] for rows with
  * 0 < row_counts[r] <= overflow_threshold, zeros otherwise.  vals bf16 / cols uint16
  * [M, ell_stride], B [K, N] bf16, C [M, N] bf16.  Replaces ell_spmm_raw

@@ -585,12 +585,101 @@ int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void
   return check_launch("b200_twell_gated_t2d_hybrid (dense rows)");
 }
 
+// ---- weight-gradient products of the training operator on the tensor cores ------------
+// out[H, D] = vals^T . rows, with vals a slab-shaped sparse [M, H] operand and rows a dense
+// [M, D] matrix: a reduction over all M tokens with a dense result, i.e. GEMM-shaped.  The
+// slab is scattered into a zero-filled K-major matrix vals_T [H, Mp], rows is transposed to
+// rows_T [D, Mp], and the one-tile GEMM above computes out[h, d] = sum_m rows_T[d, m] *
+// vals_T[h, m] (features = D on the TMEM lanes, "tokens" = H on the columns).
+
+// rows [M, D] -> rows_T [D, Mp], columns M..Mp-1 zero.  32 x 32 tiles through shared memory.
+__global__ void __launch_bounds__(256)
+transpose_pad_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int M,
+                     int D, int Mp) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  const int m0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+#pragma unroll
+  for (int r = ty; r < 32; r += 8) {
+    const int m = m0 + r;
+    tile[r][tx] = (m < M) ? in[(size_t)m * D + d0 + tx] : __float2bfloat16(0.f);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = ty; r < 32; r += 8) {
+    const int m = m0 + tx;
+    if (m < Mp) out[(size_t)(d0 + r) * Mp + m] = tile[tx][r];
+  }
+}
+
+// One warp per token row: vals_T[col, row] = value for every stored entry of the row.
+__global__ void __launch_bounds__(256)
+scatter_slab_transposed_kernel(const uint32_t* __restrict__ slab, __nv_bfloat16* __restrict__ vals_t,
+                               int M, int tiles, int slab_w, int Mp) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const uint32_t* prow = slab + (size_t)row * tiles * slab_w;
+  for (int t = 0; t < tiles; ++t) {
+    const uint32_t* s = prow + (size_t)t * slab_w;
+    const int n = min(max((int)s[0], 0), slab_w - 1);
+    for (int e = lane; e < n; e += 32) {
+      const uint32_t w = s[1 + e];
+      vals_t[(size_t)(w & 0xFFFFu) * Mp + row] = __ushort_as_bfloat16((unsigned short)(w >> 16));
+    }
+  }
+}
+
 }  // namespace
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" {
+
+size_t b200_hybrid_wgrad_workspace_bytes(int64_t M, int64_t D, int64_t H) {
+  if (M <= 0 || D <= 0 || H <= 0) return 0;
+  const int64_t Mp = (M + 63) / 64 * 64;
+  return align256((size_t)D * Mp * 2) + align256((size_t)H * Mp * 2);
+}
+
+int b200_hybrid_wgrad_dense(const void* vals_slab, const void* rows, void* out, int64_t M,
+                            int64_t D, int64_t H, int cf, int reuse_rows_t, void* ws,
+                            size_t ws_bytes, void* stream) {
+  const char* fn = "b200_hybrid_wgrad_dense";
+  if (int rc = check_dims(fn, M, D, H, cf)) return rc;
+  if (M == 0) return fail(B200_EINVAL, "%s: M must be > 0", fn);
+  if (M > (int64_t)1 << 22) return fail(B200_EUNSUPPORTED, "%s: M > 2^22 rows", fn);
+  const void* ptrs[4] = {vals_slab, rows, out, ws};
+  const char* names[4] = {"vals_slab", "rows", "out", "ws"};
+  for (int i = 0; i < 4; ++i) {
+    if (ptrs[i] == nullptr) return fail(B200_ENULL, "%s: %s is NULL", fn, names[i]);
+    if (!aligned16(ptrs[i])) return fail(B200_EALIGN, "%s: %s is not 16-byte aligned", fn, names[i]);
+  }
+  if (reinterpret_cast<uintptr_t>(ws) & 255u)
+    return fail(B200_EALIGN, "%s: ws is not 256-byte aligned", fn);
+  if (ws_bytes < b200_hybrid_wgrad_workspace_bytes(M, D, H))
+    return fail(B200_EWORKSPACE, "%s: ws holds %zu bytes, %zu needed", fn, ws_bytes,
+                b200_hybrid_wgrad_workspace_bytes(M, D, H));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t Mp = (M + 63) / 64 * 64;
+  __nv_bfloat16* rows_t = static_cast<__nv_bfloat16*>(ws);
+  __nv_bfloat16* vals_t = reinterpret_cast<__nv_bfloat16*>(static_cast<unsigned char*>(ws) +
+                                                          align256((size_t)D * Mp * 2));
+  if (!reuse_rows_t) {
+    dim3 grid((unsigned)((Mp + 31) / 32), (unsigned)(D / 32), 1);
+    transpose_pad_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(rows), rows_t,
+                                               (int)M, (int)D, (int)Mp);
+  }
+  cudaError_t e = cudaMemsetAsync(vals_t, 0, (size_t)H * Mp * 2, st);
+  if (e != cudaSuccess) return fail(B200_ECUDA, "%s: cudaMemsetAsync: %s", fn, cudaGetErrorString(e));
+  scatter_slab_transposed_kernel<<<(unsigned)((M + 7) / 8), 256, 0, st>>>(
+      static_cast<const uint32_t*>(vals_slab), vals_t, (int)M, (int)(H / kTileN), kTileN / cf,
+      (int)Mp);
+  if (int rc = check_launch(fn)) return rc;
+  return launch_dense_gemm<false>(rows_t, rows_t, D, vals_t, H, Mp, nullptr, out, nullptr, nullptr,
+                                  D, H, st);
+}
 
 size_t b200_twell_hybrid_workspace_bytes(int64_t M, int64_t D, int64_t H, int64_t dense_cap) {
   if (M <= 0 || D <= 0 || H <= 0 || dense_cap <= 0) return 0;

@@ -44,9 +44,18 @@ def ops():
     torch.ops.sparse_ops_config.set_ell_width_regular(128)
 
 
+@pytest.fixture(params=["sparse", "dense"])
+def wgrad_mode(request):
+    """Both forms of the weight-gradient products: column lists + transposed SpMM, and
+    scatter + tcgen05 GEMM (the automatic choice depends on the token count)."""
+    sparse_ops.set_weight_gradient_mode(request.param)
+    yield request.param
+    sparse_ops.set_weight_gradient_mode("auto")
+
+
 @pytest.mark.parametrize("b,s,d,h,density", [(2, 12, 256, 512, 0.06), (2, 64, 1024, 4096, 0.02),
-                                            (1, 33, 512, 1024, 0.10)])
-def test_forward_and_backward_match_dense_autograd(b, s, d, h, density):
+                                            (1, 33, 512, 1024, 0.10), (4, 640, 512, 2048, 0.03)])
+def test_forward_and_backward_match_dense_autograd(b, s, d, h, density, wgrad_mode):
     ffn = synthetic.make_ffn(d, h, seed=21, density=density, skew_sigma=0.5)
     x = synthetic.make_tokens(b * s, d, seed=22).reshape(b, s, d)
     gout = synthetic.make_tokens(b * s, d, seed=23, fold_bias=False).reshape(b, s, d)
@@ -72,7 +81,7 @@ def test_forward_and_backward_match_dense_autograd(b, s, d, h, density):
     assert int(cnt.item()) == 0
 
 
-def test_against_gradients_produced_by_the_reference(golden_dir):
+def test_against_gradients_produced_by_the_reference(golden_dir, wgrad_mode):
     g = np.load(golden_dir / "training_gated.npz")
     b, s, d, h = (int(g[k]) for k in ("b", "s", "d", "h"))
     ffn = synthetic.make_ffn(d, h, seed=int(g["seed_ffn"]), density=0.06, skew_sigma=0.5)
