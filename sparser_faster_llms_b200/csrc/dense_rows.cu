@@ -558,8 +558,9 @@ int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void
   //   one-tile CTAs, two per SM              858 / 1118 / 1148 / 1108
   //   persistent, two accumulator pairs      921 / 1042 /  896 /  893   (one CTA per SM)
   //   persistent, one pair, two CTAs per SM  852 / 1041 / 1127 / 1069
-  // All are bound by the L2 -> SM operand stream (about 64 GB/s per SM through TMA), and two
-  // CTAs per SM keep more loads in flight than one deep ring.  The one-tile form is used when
+  // All are bound by the L2 -> SM operand stream, which is latency-bound (about 1.3 us times
+  // the bytes in flight per SM: 49 GB/s per SM with 64 KB in flight, 94-112 GB/s with 128 KB),
+  // and two CTAs per SM keep more loads in flight than one ring.  The one-tile form is used when
   // the host knows the row count; when the count lives on the device (routing) the
   // persistent two-CTA form is used, because it launches no CTA per empty tile.
   const int feature_tiles = (int)(a_rows / (DUAL ? 128 : 256));
