@@ -53,6 +53,9 @@ __device__ int g_dense_error = 0;
 #ifndef B200_DENSE_PERSISTENT
 #define B200_DENSE_PERSISTENT (-1)
 #endif
+#ifndef B200_DENSE_KS
+#define B200_DENSE_KS 64
+#endif
 constexpr int kDenseTok = B200_DENSE_TOK;
 constexpr int kDenseStages = B200_DENSE_STAGES;
 
@@ -149,15 +152,17 @@ gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ rows,
 //   !DUAL: A0 / A1 = rows [256 t, +128) and [256 t + 128, +128) of one matrix
 //          (grid.x = N_out / 256); epilogue out[row_ids[token], feature] = acc (ld_out = N_out).
 // grid.y = token tiles of the capacity; tiles at or beyond *n_rows_ptr return at once.
-template <int NTOK, int STAGES, bool DUAL>
+template <int NTOK, int STAGES, bool DUAL, int KS>
 __global__ void __launch_bounds__(kThreadsTc, B200_DENSE_MINB)
 dense_rows_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
                        const __grid_constant__ CUtensorMap tmap_a1,
                        const __grid_constant__ CUtensorMap tmap_b, const float* __restrict__ bias,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ row_ids,
                        const int* __restrict__ n_rows_ptr, int n_rows_host, int K, int ld_out) {
-  constexpr int kBTileBytes = NTOK * 128;
-  constexpr int kStageBytes = 2 * kATileBytes + kBTileBytes;
+  // KS k-values per stage: 64 (128-byte rows, 128-byte swizzle) or 32 (64-byte rows and swizzle)
+  constexpr int kATile = 128 * KS * 2;
+  constexpr int kBTileBytes = NTOK * KS * 2;
+  constexpr int kStageBytes = 2 * kATile + kBTileBytes;
   constexpr uint32_t kTmemCols = 2 * NTOK;
   constexpr uint32_t kIdesc = umma_idesc(128, NTOK);
 
@@ -175,7 +180,7 @@ dense_rows_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x;
-  const int ksteps = K / kStageK;
+  const int ksteps = K / KS;
   const int a0_row = DUAL ? tile * 128 : tile * 256;
   const int a1_row = DUAL ? tile * 128 : tile * 256 + 128;
 
@@ -212,10 +217,10 @@ dense_rows_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
         }
         unsigned char* st = smem + (size_t)s * kStageBytes;
         mbar_expect_tx(&full_bar[s], (uint32_t)kStageBytes);
-        tma_load_2d(st, &tmap_a0, k * kStageK, a0_row, &full_bar[s]);
-        tma_load_2d(st + kATileBytes, DUAL ? &tmap_a1 : &tmap_a0, k * kStageK, a1_row,
+        tma_load_2d(st, &tmap_a0, k * KS, a0_row, &full_bar[s]);
+        tma_load_2d(st + kATile, DUAL ? &tmap_a1 : &tmap_a0, k * KS, a1_row,
                     &full_bar[s]);
-        tma_load_2d(st + 2 * kATileBytes, &tmap_b, k * kStageK, m0, &full_bar[s]);
+        tma_load_2d(st + 2 * kATile, &tmap_b, k * KS, m0, &full_bar[s]);
       }
     }
   } else if (warp == 1) {
@@ -230,10 +235,11 @@ dense_rows_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a0 = smem_u32(smem + (size_t)s * kStageBytes);
-        const uint64_t da0 = umma_desc(a0), da1 = umma_desc(a0 + kATileBytes),
-                       db = umma_desc(a0 + 2 * kATileBytes);
+        const uint64_t da0 = KS == 64 ? umma_desc(a0) : umma_desc_sw64(a0),
+                       da1 = KS == 64 ? umma_desc(a0 + kATile) : umma_desc_sw64(a0 + kATile),
+                       db = KS == 64 ? umma_desc(a0 + 2 * kATile) : umma_desc_sw64(a0 + 2 * kATile);
 #pragma unroll
-        for (int kk = 0; kk < kStageK / 16; ++kk) {
+        for (int kk = 0; kk < KS / 16; ++kk) {
           const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
           umma_bf16(tmem_base, da0 + 2 * kk, db + 2 * kk, kIdesc, acc);
           umma_bf16(tmem_base + NTOK, da1 + 2 * kk, db + 2 * kk, kIdesc, acc);
@@ -574,9 +580,19 @@ int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void
   if (form == 2)
     return launch_persistent<2, 1, DUAL>(map_a0, map_a1, map_b, bias, out, row_ids, n_rows_ptr, cap,
                                          K, ld_out, feature_tiles, tiles_max, stream);
-  constexpr int STAGES = kDenseStages;
-  const size_t smem = (size_t)STAGES * (2 * kATileBytes + kDenseTok * 128) + 1024;
-  auto kern = dense_rows_gemm_kernel<kDenseTok, STAGES, DUAL>;
+  // Stage depth in K of the one-tile form: 64 k-values x 2 stages, or (B200_DENSE_KS=32)
+  // 32 x 4 in the same shared memory with 64-byte swizzle.  The finer stages keep more bytes
+  // in flight but double the barrier round trips of the single MMA-issuing thread: measured
+  // 861 vs 1107 TFLOP/s at M = 16384, D = 2048, H = 11008, so 64 stays the default.
+  constexpr int KS = B200_DENSE_KS;
+  constexpr int STAGES = kDenseStages * (64 / KS);
+  if (KS != 64) {
+    if (int rc = make_map(&map_a0, a0, a_rows, K, 128, KS)) return rc;
+    if (int rc = make_map(&map_a1, a1, a_rows, K, 128, KS)) return rc;
+    if (int rc = make_map(&map_b, b, b_rows, K, kDenseTok, KS)) return rc;
+  }
+  const size_t smem = (size_t)STAGES * (2 * 128 * KS * 2 + kDenseTok * KS * 2) + 1024;
+  auto kern = dense_rows_gemm_kernel<kDenseTok, STAGES, DUAL, KS>;
   static size_t granted[64] = {0};
   if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_gated_t2d_hybrid")) return rc;
   dim3 grid((unsigned)(a_rows / (DUAL ? 128 : 256)), (unsigned)((cap + kDenseTok - 1) / kDenseTok), 1);

@@ -67,6 +67,17 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
   return d;
 }
 
+// The same for tiles of 32 k-values (64 bytes per row): 64-byte swizzle, 8-row groups 512 B apart.
+__device__ __forceinline__ uint64_t umma_desc_sw64(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;                     // SWIZZLE_64B
+  return d;
+}
+
 // Instruction descriptor, kind::f16: fp32 accumulate, bf16 x bf16, both operands K-major.
 __host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
@@ -144,16 +155,19 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [rows, K] bf16 row-major; box = 64 k-values x box_rows rows, 128-byte swizzle, zero fill.
-inline int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int box_rows) {
+// [rows, K] bf16 row-major; box = box_k (64 or 32) k-values x box_rows rows with the 128- or
+// 64-byte swizzle that matches the row length, zero fill.
+inline int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int box_rows,
+                    int box_k = kStageK) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(B200_ECUDA, "tensor map: cuTensorMapEncodeTiled unavailable");
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kStageK, (cuuint32_t)box_rows};
+  const cuuint32_t box[2] = {(cuuint32_t)box_k, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  box_k == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(B200_ECUDA, "tensor map: cuTensorMapEncodeTiled failed (%d)", (int)r);
