@@ -58,9 +58,9 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--eager-collectives", action="store_true",
                     help="multi-rank: launch the step eagerly instead of as one CUDA graph")
-    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
-                    help="multi-rank: sum the partial outputs with the library's peer-memory "
-                         "all-reduce kernel (default) or with NCCL")
+    ap.add_argument("--collective", default="fused", choices=["fused", "peer", "nccl"],
+                    help="multi-rank: sum the partial outputs inside the contraction kernel "
+                         "(default), with the library's peer-memory all-reduce kernel, or with NCCL")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch eagerly instead of replaying a CUDA graph (for profilers)")
     return ap.parse_args()
@@ -212,14 +212,21 @@ def make_peer_allreduce(args, device, dist_on):
         return None, "nccl all-reduce"
     import torch.distributed as dist
     from sparser_faster_llms_b200 import peer_allreduce
-    par, why = None, ""
+    par, far, why = None, None, ""
     try:
         par = peer_allreduce.PeerAllReduce(args.batch * args.d_model * 2, device=device)
+        if args.collective == "fused" and args.batch <= 256:
+            far = peer_allreduce.FusedShardAllReduce(args.batch, args.d_model, device=device)
     except Exception as exc:  # symmetric memory not available on this box
         why = f"{type(exc).__name__}: {exc}"[:160]
+        par = far = None
     ok = torch.tensor([1 if par is not None else 0], device=device)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if int(ok.item()) == 1:
+        par.fused = far
+        if far is not None:
+            return par, ("contraction fused with the shard all-reduce over peer memory "
+                         "(b200_twell_gated_mlp_allreduce)")
         return par, "peer-memory all-reduce kernel (b200_peer_allreduce_bf16)"
     return None, f"nccl all-reduce (peer all-reduce unavailable: {why or 'on another rank'})"
 
@@ -249,10 +256,17 @@ def run_ours(args):
     ws = (ws_buf.data_ptr(), ws_buf.numel())
 
     par, collective = make_peer_allreduce(args, device, dist_on)
+    far = getattr(par, "fused", None)
     part = torch.empty(B, d, device=device, dtype=torch.bfloat16) if par is not None else None
 
     def step():
         for l, (g, u, dn) in enumerate(layers):
+            if far is not None:  # one pack kernel + one contraction-and-all-reduce kernel
+                _lib.call("b200_twell_gated_mlp_allreduce", device, x[l].data_ptr(), g.data_ptr(),
+                          None, u.data_ptr(), dn.data_ptr(), packed.data_ptr(),
+                          out[l].data_ptr(), B, d, hl, 8, 0, *ws, far.ptr_array, far.rank,
+                          far.world, far.block_bytes)
+                continue
             y = out[l] if par is None else part
             _lib.call("b200_twell_gated_mlp", device, x[l].data_ptr(), g.data_ptr(), None,
                       u.data_ptr(), dn.data_ptr(), packed.data_ptr(), y.data_ptr(),
@@ -335,7 +349,7 @@ def run_ours(args):
                      # (profiles/decode_ffn_batch32_pack_and_contraction.md), scaled to this launch
                      "traffic": float(pack_bytes),
                      "us_per_launch": ms_pack * 1e3, "algorithmic_bytes": pack_bytes},
-        "gpu_launches": args.steps * L * (3 if par is not None else 2),
+        "gpu_launches": args.steps * L * (3 if (par is not None and far is None) else 2),
         "clocks": clocks,
     }
 
@@ -371,6 +385,8 @@ def run_ours(args):
     if par is not None:
         # non-zero: a bounded wait on a peer gave up somewhere in the run (results invalid)
         result["config"]["peer_allreduce_status"] = par.status()
+        if far is not None:
+            result["config"]["fused_allreduce_status"] = far.status()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(args, sample_layers=2, reps=3)
     if rank == 0:
@@ -396,6 +412,7 @@ def run_e2e(args, layers, x, device, dist_on, par=None):
     if dist_on:
         mods = [sharded.ShardedTwELLGatedMLP(1000 + l, g, u, dn, presharded=True,
                                              peer_allreduce=par,
+                                             fused_allreduce=getattr(par, "fused", None),
                                              preallocate_shared_hidden_state=True)
                 for l, (g, u, dn) in enumerate(layers)]
     else:

@@ -302,6 +302,39 @@ int b200_peer_allreduce_bf16(const void* local_in, void* out, int64_t n_elems,
  * clears the word; synchronises the device. */
 int b200_peer_allreduce_status(void* my_block);
 
+/* ------------------------------------------------------------------------
+ * Gated contraction fused with the d_ff-shard all-reduce (no reference counterpart).
+ * The CTA that holds the final sums of a (token, column slice) rounds them to bf16, sends
+ * them to every peer as 8-byte {bf16 pair, call epoch} words, polls - bounded - its own
+ * inbox for the peers' words, adds the `world` contributions in rank order and stores:
+ * the same result as b200_twell_gated_t2d + b200_peer_allreduce_bf16 in one kernel.
+ * Decode-sized calls only: every CTA must be resident while it waits (M * clusters <= 2 x SMs)
+ * and M <= 256; larger calls return B200_EUNSUPPORTED (use the two-kernel form).
+ * peer_blocks: `world` device pointers to symmetric, peer-mapped blocks of
+ * b200_fused_allreduce_block_bytes(max_tokens, D) bytes, zero-filled once, used by this
+ * entry point only.  All ranks issue the same sequence of calls.  Capturable.
+ * world == 1 degenerates to b200_twell_gated_t2d.
+ * ------------------------------------------------------------------------ */
+size_t b200_fused_allreduce_block_bytes(int64_t max_tokens, int64_t D);
+
+int b200_twell_gated_t2d_allreduce(const void* x, const void* packed, const void* up,
+                                   const void* down, void* out, int64_t M, int64_t D, int64_t H,
+                                   int cf, uint32_t flags, void* workspace, size_t workspace_bytes,
+                                   void* const* peer_blocks, int rank, int world,
+                                   int64_t block_bytes, void* stream);
+
+/* b200_twell_pack followed by b200_twell_gated_t2d_allreduce. */
+int b200_twell_gated_mlp_allreduce(const void* x, const void* gate, const float* gate_bias,
+                                   const void* up, const void* down, void* packed, void* out,
+                                   int64_t M, int64_t D, int64_t H, int cf, uint32_t flags,
+                                   void* workspace, size_t workspace_bytes,
+                                   void* const* peer_blocks, int rank, int world,
+                                   int64_t block_bytes, void* stream);
+
+/* 0, or 0x100 + peer rank if a wait for that peer gave up; -1 if unreadable.  Reads and
+ * clears the word; synchronises the device. */
+int b200_fused_allreduce_status(void* my_block);
+
 /*
  * Gated contraction for hosts that may not allocate device memory (no counterpart
  * in the reference).  Same arguments and result as b200_twell_gated_t2d, minus the

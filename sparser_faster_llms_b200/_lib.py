@@ -71,6 +71,17 @@ _PROTOTYPES = {
     "b200_twell_hybrid_counters": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64,
                                            ctypes.POINTER(c_int)]),
     "b200_twell_hybrid_status": (c_int, []),
+    "b200_fused_allreduce_block_bytes": (c_size_t, [c_int64, c_int64]),
+    # x, packed, up, down, out, M, D, H, cf, flags, ws, ws_bytes, peer_blocks, rank, world,
+    # block_bytes, stream
+    "b200_twell_gated_t2d_allreduce": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_int64, c_int,
+                                               c_uint32, c_void_p, c_size_t, c_void_p, c_int,
+                                               c_int, c_int64, c_void_p]),
+    # x, gate, gate_bias, up, down, packed, out, then as above
+    "b200_twell_gated_mlp_allreduce": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int64, c_int,
+                                               c_uint32, c_void_p, c_size_t, c_void_p, c_int,
+                                               c_int, c_int64, c_void_p]),
+    "b200_fused_allreduce_status": (c_int, [c_void_p]),
     "b200_peer_allreduce_block_bytes": (c_size_t, [c_int64]),
     "b200_peer_allreduce_bf16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int,
                                          c_int64, c_void_p]),

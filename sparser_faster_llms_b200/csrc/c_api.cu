@@ -38,7 +38,7 @@ int twell_pack_tc_status();
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
                      void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream,
-                     const unsigned char* skip_rows = nullptr);
+                     const unsigned char* skip_rows = nullptr, const FusedAr* fused_ar = nullptr);
 
 bool pdl_enabled() {
   static int state = -1;
@@ -191,6 +191,70 @@ int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias
   B200_TRY(b200_twell_pack(x, gate, gate_bias, packed, M, D, H, cf, stream));
   return b200_twell_gated_t2d(x, packed, up, down, out, M, D, H, cf, flags, workspace,
                               workspace_bytes, stream);
+}
+
+size_t b200_fused_allreduce_block_bytes(int64_t max_tokens, int64_t D) {
+  if (max_tokens <= 0 || D <= 0) return 0;
+  const size_t slot = ((size_t)max_tokens * (size_t)D * 4 + 255) & ~(size_t)255;
+  return kFarControlBytes + 2 * 8 * slot;
+}
+
+int b200_twell_gated_t2d_allreduce(const void* x, const void* packed, const void* up,
+                                   const void* down, void* out, int64_t M, int64_t D, int64_t H,
+                                   int cf, uint32_t flags, void* workspace, size_t workspace_bytes,
+                                   void* const* peer_blocks, int rank, int world,
+                                   int64_t block_bytes, void* stream) {
+  const char* fn = "b200_twell_gated_t2d_allreduce";
+  B200_TRY(check_dims(fn, M, D, H, cf));
+  if (flags & ~B200_FLAG_HIGH_PRECISION) return fail(B200_EINVAL, "%s: unknown flags 0x%x", fn, flags);
+  if (world < 1 || world > 8 || rank < 0 || rank >= world)
+    return fail(B200_EINVAL, "%s: need 1 <= world <= 8 and 0 <= rank < world", fn);
+  if (M == 0) return B200_OK;
+  B200_TRY(check_ptr(fn, "x", x));
+  B200_TRY(check_ptr(fn, "packed", packed));
+  B200_TRY(check_ptr(fn, "up", up));
+  B200_TRY(check_ptr(fn, "down", down));
+  B200_TRY(check_ptr(fn, "out", out));
+  B200_TRY(check_workspace(fn, workspace));
+  FusedAr ar = {};
+  ar.rank = rank;
+  ar.world = world;
+  if (world > 1) {
+    if (peer_blocks == nullptr) return fail(B200_ENULL, "%s: peer_blocks is NULL", fn);
+    if (block_bytes <= (int64_t)kFarControlBytes)
+      return fail(B200_EWORKSPACE, "%s: block_bytes too small", fn);
+    ar.slot_bytes = ((block_bytes - (int64_t)kFarControlBytes) / 16) & ~(int64_t)255;
+    for (int r = 0; r < world; ++r) {
+      B200_TRY(check_ptr(fn, "peer block", peer_blocks[r]));
+      ar.block[r] = static_cast<unsigned char*>(peer_blocks[r]);
+    }
+  }
+  return twell_t2d_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, packed, up, down, out,
+                          M, D, H, cf, workspace, workspace_bytes, sm_count(),
+                          static_cast<cudaStream_t>(stream), nullptr, &ar);
+}
+
+int b200_twell_gated_mlp_allreduce(const void* x, const void* gate, const float* gate_bias,
+                                   const void* up, const void* down, void* packed, void* out,
+                                   int64_t M, int64_t D, int64_t H, int cf, uint32_t flags,
+                                   void* workspace, size_t workspace_bytes,
+                                   void* const* peer_blocks, int rank, int world,
+                                   int64_t block_bytes, void* stream) {
+  B200_TRY(b200_twell_pack(x, gate, gate_bias, packed, M, D, H, cf, stream));
+  return b200_twell_gated_t2d_allreduce(x, packed, up, down, out, M, D, H, cf, flags, workspace,
+                                        workspace_bytes, peer_blocks, rank, world, block_bytes,
+                                        stream);
+}
+
+/* Reads and clears the error word of this rank's fused all-reduce block (0 = no wait ever
+ * gave up, else 0x100 + the peer that did not arrive).  Synchronises the device. */
+int b200_fused_allreduce_status(void* my_block) {
+  if (my_block == nullptr) return -1;
+  uint32_t v = 0, zero = 0;
+  uint32_t* p = static_cast<uint32_t*>(my_block) + kFarErrorWord;
+  if (cudaMemcpy(&v, p, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpy(p, &zero, 4, cudaMemcpyHostToDevice);
+  return (int)v;
 }
 
 int b200_twell_mlp(const void* x, const void* up, const void* down, void* packed, void* out,

@@ -87,6 +87,19 @@ inline unsigned add_pdl_attribute(cudaLaunchAttribute* attrs, unsigned n) {
   return n + 1;
 }
 
+// Peer blocks of the contraction fused with the d_ff-shard all-reduce (twell_t2d.cu).
+// world <= 1 means "not fused".
+struct FusedAr {
+  unsigned char* block[8];
+  int rank, world;
+  long long slot_bytes;  // bytes of one (parity, source rank) inbox slot: 8 per bf16 pair
+};
+constexpr int kFarEpochWord = 0;            // epoch of the last finished call
+constexpr int kFarDoneWord = 1;             // (token, slice) groups of the running call that finished
+constexpr int kFarErrorWord = 2;            // set when a wait for a peer gave up
+constexpr size_t kFarControlBytes = 1024;   // control words, padding; the inbox follows
+constexpr int kFarMaxTokens = 256;
+
 __device__ __forceinline__ uint32_t bf16_bits(float v) {
   return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
 }

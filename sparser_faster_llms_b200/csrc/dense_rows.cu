@@ -28,7 +28,7 @@ namespace b200 {
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
                      void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream,
-                     const unsigned char* skip_rows);
+                     const unsigned char* skip_rows, const FusedAr* fused_ar);
 int sm_count();
 
 namespace {
@@ -740,7 +740,7 @@ int b200_twell_gated_t2d_hybrid(const void* x, const void* packed, const void* g
   if (int rc = check_launch(fn)) return rc;
   if (int rc = twell_t2d_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, packed, up, down,
                                 out, M, D, H, cf, workspace, workspace_bytes, sm_count(), st,
-                                w.flags))
+                                w.flags, nullptr))
     return rc;
   gather_rows_kernel<<<(unsigned)dense_cap, 256, 0, st>>>(
       static_cast<const uint4*>(x), w.rows, w.counters, reinterpret_cast<uint4*>(w.xd),

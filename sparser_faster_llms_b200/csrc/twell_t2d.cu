@@ -48,6 +48,64 @@ __device__ __forceinline__ uint4 ldg_nc(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
 }
 
+// ---- contraction fused with the d_ff-shard all-reduce ------------------------------
+// With world > 1 the CTA that holds the final sums of a (token, column slice) does not store
+// them: it rounds them to bf16 (exactly what the unfused path would have stored), sends each
+// bf16 pair to every peer GPU as one 8-byte word {pair, call epoch} (plain peer stores into
+// the peers' inboxes; no fence, no TMA, no multicast), polls its own inbox - bounded - for
+// the peers' words of the same pairs, adds the world contributions in rank order in fp32 and
+// only then stores bf16.  Same result as contraction + b200_peer_allreduce_bf16, one kernel
+// and one pass over `out` less.  Block layout per rank (symmetric):
+//   word 0 epoch of the last finished call, word 1 finished (token, slice) groups of the
+//   running call, word 2 error word; from 1 KB on inbox[parity][source rank][pair] of uint2,
+//   pair = (token * D + column) / 2 - independent of how the call is cut into CTAs.
+// The inbox is double-buffered by the epoch's parity (a pair is rewritten two calls later,
+// which a peer can reach only after this rank has finished the call in between).
+constexpr uint32_t kFarSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t bf162_bits(__nv_bfloat162 v) {
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void far_push(const FusedAr& ar, size_t inbox_off, size_t pair,
+                                         uint32_t payload, uint32_t e) {
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    if (p >= ar.world || p == ar.rank) continue;
+    uint2* dst = reinterpret_cast<uint2*>(ar.block[p] + inbox_off +
+                                          (size_t)ar.rank * (size_t)ar.slot_bytes) + pair;
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(payload), "r"(e)
+                 : "memory");
+  }
+}
+
+// Sum over ranks, in rank order, of the bf16 pairs of one position; `mine` is this rank's.
+__device__ __forceinline__ float2 far_gather(const FusedAr& ar, const unsigned char* my_inbox,
+                                             size_t pair, uint32_t mine, uint32_t e,
+                                             uint32_t* err) {
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    if (p >= ar.world) continue;
+    uint32_t payload = mine;
+    if (p != ar.rank) {
+      const uint2* src = reinterpret_cast<const uint2*>(my_inbox + (size_t)p * (size_t)ar.slot_bytes) + pair;
+      uint32_t flag = 0, spins = 0;
+      do {
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
+                     : "=r"(payload), "=r"(flag)
+                     : "l"(src)
+                     : "memory");
+      } while (flag != e && ++spins < kFarSpinLimit);
+      if (flag != e) atomicExch(err, 0x100u + (uint32_t)p);  // this peer never arrived
+    }
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&payload));
+    s0 += f.x;
+    s1 += f.y;
+  }
+  return make_float2(s0, s1);
+}
+
 // NI = D / 256 = warps per CTA.
 // grid.x = M * nc * cs, cluster = cs.  ws_partial: [M][nc][D] fp32, ws_counter: [M][8] (nc > 1).
 template <int NI, bool GATED, bool HP>
@@ -56,7 +114,8 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
                  const __nv_bfloat16* __restrict__ up, const __nv_bfloat16* __restrict__ down,
                  __nv_bfloat16* out, int M, int tiles, int slab_w, int cs, int nc,
                  float* ws_partial, unsigned int* ws_counter,
-                 const unsigned char* __restrict__ skip_rows) {
+                 const unsigned char* __restrict__ skip_rows,
+                 const __grid_constant__ FusedAr ar) {
   constexpr int D = NI * 256;
   constexpr int NTHREADS = NI * 32;
   __shared__ int tile_off[kMaxTiles + 1];
@@ -64,6 +123,7 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
   __shared__ float usum[2][GATED ? kDepth : 1][GATED ? NI : 1];  // double-buffered per batch
   __shared__ __align__(16) float inbox[D];  // [cs][D / cs]: column sums pushed by the cluster
   __shared__ int is_last;
+  __shared__ uint32_t epoch_s;
   __shared__ __align__(16) uint32_t slab_s[kStageWords];
 
   cg::cluster_group cluster = cg::this_cluster();
@@ -76,6 +136,16 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
   // Rows routed to the dense tensor-core path: every CTA of every cluster of the row leaves
   // (the row is uniform per cluster, so no cluster barrier is left half-attended).
   if (skip_rows != nullptr && skip_rows[row]) return;
+  // Fused all-reduce: every CTA reads the call epoch now (the round trip hides under the slab
+  // load).  It is advanced by the last (token, slice) group to finish, which cannot happen
+  // before every CTA of the grid has contributed its partial sums, i.e. has started.
+  const bool fused = ar.world > 1;
+  unsigned char* my_block = nullptr;
+#pragma unroll
+  for (int p = 0; p < 8; ++p)
+    if (p == ar.rank) my_block = ar.block[p];
+  if (fused && tid == 0)
+    epoch_s = reinterpret_cast<volatile uint32_t*>(my_block)[kFarEpochWord] + 1u;
   const uint32_t* prow = packed + (size_t)row * tiles * slab_w;
   // Remote shared memory may only be touched once every CTA of the cluster runs:
   // arrive now, wait right before the first remote store.
@@ -264,16 +334,59 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
   cluster.sync();
 
   __nv_bfloat16* orow = out + (size_t)row * D + crank * cols;
+  // Final sums of a column pair: stored, or (fused all-reduce) sent to the peers and kept.
+  // A thread finishes at most 4 pairs (cols <= D = 8 * NTHREADS), pair k at column
+  // c = 2 * (tid + k * NTHREADS).
+  const uint32_t e = fused ? epoch_s : 0u;
+  const size_t inbox_off = kFarControlBytes + (size_t)(e & 1u) * 8 * (size_t)ar.slot_bytes;
+  const size_t pair0 = ((size_t)row * D + (size_t)crank * cols) >> 1;
+  __nv_bfloat162 mine[4];
+  auto emit = [&](int k, int c, float s0, float s1) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(s0, s1);
+    if (!fused) {
+      *reinterpret_cast<__nv_bfloat162*>(orow + c) = v;
+    } else {
+      mine[k] = v;
+      far_push(ar, inbox_off, pair0 + (c >> 1), bf162_bits(v), e);
+    }
+  };
+  // Fused: wait for the peers' pairs, add in rank order, store.  The last of the M * cs
+  // finishing CTAs of the call advances the call epoch.
+  auto collect = [&]() {
+    if (!fused) return;
+    uint32_t* ctl = reinterpret_cast<uint32_t*>(my_block);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = 2 * (tid + k * NTHREADS);
+      if (c >= cols) break;
+      const float2 s = far_gather(ar, my_block + inbox_off, pair0 + (c >> 1), bf162_bits(mine[k]),
+                                  e, ctl + kFarErrorWord);
+      *reinterpret_cast<__nv_bfloat162*>(orow + c) = __floats2bfloat162_rn(s.x, s.y);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const uint32_t done = atomicAdd(ctl + kFarDoneWord, 1u);
+      if (done == (uint32_t)(M * cs) - 1u) {
+        ctl[kFarDoneWord] = 0u;
+        __threadfence();
+        reinterpret_cast<volatile uint32_t*>(ctl)[kFarEpochWord] = e;
+      }
+    }
+  };
   if (nc == 1) {
-    for (int c = tid * 2; c < cols; c += NTHREADS * 2) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = 2 * (tid + k * NTHREADS);
+      if (c >= cols) break;
       float s0 = 0.f, s1 = 0.f;
       for (int q = 0; q < cs; ++q) {
         const float2 v = *reinterpret_cast<const float2*>(inbox + (size_t)q * cols + c);
         s0 += v.x;
         s1 += v.y;
       }
-      *reinterpret_cast<__nv_bfloat162*>(orow + c) = __floats2bfloat162_rn(s0, s1);
+      emit(k, c, s0, s1);
     }
+    collect();
     return;
   }
 
@@ -298,22 +411,27 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
   if (!is_last) return;
   __threadfence();
   const float* tok_part = ws_partial + (size_t)row * nc * D + crank * cols;
-  for (int c = tid * 2; c < cols; c += NTHREADS * 2) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = 2 * (tid + k * NTHREADS);
+    if (c >= cols) break;
     float s0 = 0.f, s1 = 0.f;
     for (int q = 0; q < nc; ++q) {
       const float2 v = __ldcg(reinterpret_cast<const float2*>(tok_part + (size_t)q * D + c));
       s0 += v.x;
       s1 += v.y;
     }
-    *reinterpret_cast<__nv_bfloat162*>(orow + c) = __floats2bfloat162_rn(s0, s1);
+    emit(k, c, s0, s1);
   }
   if (tid == 0) ws_counter[row * 8 + crank] = 0u;  // ready for the next launch
+  collect();
 }
 
 template <int NI, bool GATED, bool HP>
 int launch_t2d(const void* x, const void* packed, const void* up, const void* down, void* out,
                int64_t M, int64_t H, int cf, int cs, int nc, float* ws_partial,
-               unsigned int* ws_counter, const unsigned char* skip_rows, cudaStream_t stream) {
+               unsigned int* ws_counter, const unsigned char* skip_rows, const FusedAr& ar,
+               cudaStream_t stream) {
   const int slab_w = kTileN / cf;
   const int tiles = (int)(H / kTileN);
   auto kern = twell_t2d_kernel<NI, GATED, HP>;
@@ -333,7 +451,7 @@ int launch_t2d(const void* x, const void* packed, const void* up, const void* do
       &cfg, kern, reinterpret_cast<const __nv_bfloat16*>(x),
       reinterpret_cast<const uint32_t*>(packed), reinterpret_cast<const __nv_bfloat16*>(up),
       reinterpret_cast<const __nv_bfloat16*>(down), reinterpret_cast<__nv_bfloat16*>(out), (int)M,
-      tiles, slab_w, cs, nc, ws_partial, ws_counter, skip_rows);
+      tiles, slab_w, cs, nc, ws_partial, ws_counter, skip_rows, ar);
   if (e != cudaSuccess) return fail(B200_ECUDA, "twell_t2d: launch: %s", cudaGetErrorString(e));
   return B200_OK;
 }
@@ -341,12 +459,13 @@ int launch_t2d(const void* x, const void* packed, const void* up, const void* do
 template <bool GATED, bool HP>
 int dispatch_ni(int ni, const void* x, const void* packed, const void* up, const void* down,
                 void* out, int64_t M, int64_t H, int cf, int cs, int nc, float* ws_partial,
-                unsigned int* ws_counter, const unsigned char* skip_rows, cudaStream_t stream) {
+                unsigned int* ws_counter, const unsigned char* skip_rows, const FusedAr& ar,
+                cudaStream_t stream) {
   switch (ni) {
 #define B200_CASE(N)                                                                           \
   case N:                                                                                      \
     return launch_t2d<N, GATED, HP>(x, packed, up, down, out, M, H, cf, cs, nc, ws_partial,   \
-                                    ws_counter, skip_rows, stream);
+                                    ws_counter, skip_rows, ar, stream);
     B200_CASE(1) B200_CASE(2) B200_CASE(3) B200_CASE(4) B200_CASE(5) B200_CASE(6) B200_CASE(7)
     B200_CASE(8) B200_CASE(9) B200_CASE(10) B200_CASE(11) B200_CASE(12) B200_CASE(13)
     B200_CASE(14) B200_CASE(15) B200_CASE(16)
@@ -384,22 +503,35 @@ void t2d_shape(int64_t M, int64_t D, int sm_count, size_t workspace_bytes, int* 
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
                      void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream,
-                     const unsigned char* skip_rows = nullptr) {
+                     const unsigned char* skip_rows = nullptr,
+                     const FusedAr* fused_ar = nullptr) {
   int cs = 1, nc = 1;
   t2d_shape(M, D, sm_count, workspace != nullptr ? workspace_bytes : 0, &cs, &nc);
+  FusedAr far = {};
+  if (fused_ar != nullptr && fused_ar->world > 1) {
+    // Every CTA must be resident while it waits for the peers.
+    if (M * nc * cs > 2 * (int64_t)sm_count || M > kFarMaxTokens)
+      return fail(B200_EUNSUPPORTED,
+                  "twell_t2d: the fused all-reduce serves at most %d tokens in one wave (M = %lld)",
+                  kFarMaxTokens, (long long)M);
+    if ((int64_t)M * D * 4 > fused_ar->slot_bytes)
+      return fail(B200_EWORKSPACE, "twell_t2d: %lld tokens do not fit the peer blocks' slots",
+                  (long long)M);
+    far = *fused_ar;
+  }
   unsigned int* counters = reinterpret_cast<unsigned int*>(workspace);
   float* partial = workspace ? reinterpret_cast<float*>(counters + kCounterWords) : nullptr;
   const int ni = (int)(D / 256);
   if (gated) {
     return hp ? dispatch_ni<true, true>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                        counters, skip_rows, stream)
+                                        counters, skip_rows, far, stream)
               : dispatch_ni<true, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                         counters, skip_rows, stream);
+                                         counters, skip_rows, far, stream);
   }
   return hp ? dispatch_ni<false, true>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                       counters, skip_rows, stream)
+                                       counters, skip_rows, far, stream)
             : dispatch_ni<false, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                        counters, skip_rows, stream);
+                                        counters, skip_rows, far, stream);
 }
 
 int sm_count();  // c_api.cu

@@ -20,6 +20,52 @@ import torch.distributed as dist
 from . import _lib
 
 
+class FusedShardAllReduce:
+    """Peer blocks for the contraction that sums the d_ff shards in its own epilogue
+    (``b200_twell_gated_mlp_allreduce``): one kernel per rank computes the shard's FFN output,
+    exchanges bf16 pairs with the peers and stores the sum.  Decode-sized calls only
+    (``max_tokens`` <= 256 and a single wave of CTAs); attach it to a layer with
+    :func:`sparser_faster_llms_b200.twell.set_d2t_layer_fused_allreduce` or pass it to
+    :class:`sparser_faster_llms_b200.sharded.ShardedTwELLGatedMLP`.  One object serves all
+    layers of a model; keep it separate from any :class:`PeerAllReduce` (own epochs, own inbox).
+    """
+
+    def __init__(self, max_tokens: int, d_model: int, *, group=None,
+                 device: torch.device | None = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        if not dist.is_initialized():
+            raise RuntimeError("FusedShardAllReduce needs an initialised process group")
+        if not 0 < max_tokens <= 256:
+            raise ValueError("max_tokens must be in 1..256")
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        if self.world > 8:
+            raise ValueError("FusedShardAllReduce supports at most 8 ranks (one node)")
+        self.device = device if device is not None else torch.device("cuda",
+                                                                     torch.cuda.current_device())
+        self.max_tokens, self.d_model = int(max_tokens), int(d_model)
+        lib = _lib.load_library()
+        self.block_bytes = int(lib.b200_fused_allreduce_block_bytes(self.max_tokens, self.d_model))
+        self.block = symm_mem.empty(self.block_bytes, dtype=torch.uint8, device=self.device)
+        self.block.zero_()
+        self.handle = symm_mem.rendezvous(self.block, self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(ptrs) != self.world:
+            raise RuntimeError("symmetric memory returned an unexpected number of peers")
+        self.ptr_array = (ctypes.c_void_p * self.world)(*ptrs)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)  # every block is zeroed before anyone may push into it
+
+    def serves(self, tokens: int, d_model: int) -> bool:
+        return tokens <= self.max_tokens and d_model == self.d_model
+
+    def status(self) -> int:
+        """0, or ``0x100 + peer`` if a wait for that peer gave up.  Synchronises the device."""
+        with torch.cuda.device(self.device):
+            return int(_lib.load_library().b200_fused_allreduce_status(self.block.data_ptr()))
+
+
 class PeerAllReduce:
     def __init__(self, max_bytes: int, *, group=None, device: torch.device | None = None):
         import torch.distributed._symmetric_memory as symm_mem

@@ -118,9 +118,14 @@ class ShardedTwELLGatedMLP(nn.Module):
                  DOWN: torch.Tensor, *, process_group=None, rank: int | None = None,
                  world_size: int | None = None, presharded: bool = False,
                  reduce_dtype: torch.dtype | None = None, peer_allreduce=None,
+                 fused_allreduce=None,
                  local_factory: Callable[..., nn.Module] | None = None, **twell_kwargs):
         super().__init__()
         self.process_group = process_group
+        # optional sparser_faster_llms_b200.peer_allreduce.FusedShardAllReduce shared by all
+        # layers: decode-sized calls sum the shards inside the contraction kernel; other calls
+        # fall back to peer_allreduce / NCCL below
+        self.fused_allreduce = fused_allreduce
         # optional sparser_faster_llms_b200.peer_allreduce.PeerAllReduce shared by all layers:
         # one peer-memory kernel instead of an NCCL all-reduce (bf16 sum, rank order)
         self.peer_allreduce = peer_allreduce
@@ -142,7 +147,30 @@ class ShardedTwELLGatedMLP(nn.Module):
         self.local = local_factory(layer_number, g, u, d, **twell_kwargs)
         self.reduce_dtype = reduce_dtype
 
+    def _fused_ready(self, A: torch.Tensor) -> bool:
+        """Attach the fused all-reduce to the local layer's cached state (created on the first
+        forward, re-created when the module is moved) and say whether it serves this call."""
+        far = self.fused_allreduce
+        if far is None or self.world_size == 1:
+            return False
+        tokens = A.numel() // A.shape[-1]
+        if not far.serves(tokens, A.shape[-1]):
+            return False
+        from . import twell
+        entry = twell._D2T_LAYERS.get(int(getattr(self.local, "layer_number", -1)))
+        if entry is None:
+            return False  # first forward: the layer state does not exist yet
+        entry["fused_allreduce"] = far
+        return True
+
     def forward(self, A: torch.Tensor) -> torch.Tensor:
+        if self._fused_ready(A):
+            return self.local(A)  # the contraction's epilogue has already summed the shards
+        if self.fused_allreduce is not None:
+            from . import twell
+            entry = twell._D2T_LAYERS.get(int(getattr(self.local, "layer_number", -1)))
+            if entry is not None:
+                entry.pop("fused_allreduce", None)  # a call the fused form does not serve
         y = self.local(A)
         if self.world_size > 1 and self.peer_allreduce is not None:
             return self.peer_allreduce.all_reduce(y.contiguous())

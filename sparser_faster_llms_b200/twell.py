@@ -440,7 +440,14 @@ def _gated_mlp(layer_number, A, UP, DOWN, C_packed, OUT, highest_precision, cf) 
     dev = _same_device(A, GATE, UP, DOWN, C_packed, OUT)
     flags = _lib.FLAG_HIGH_PRECISION if highest_precision else 0
     route = entry.get("dense_route")
-    if (route is not None and route["dense_all_tokens"] is not None
+    far = entry.get("fused_allreduce")
+    if far is not None and far.serves(m, d):
+        # d_ff shard: the contraction sums the shards in its own epilogue (one kernel per rank)
+        _lib.call("b200_twell_gated_mlp_allreduce", dev, A.data_ptr(), GATE.data_ptr(),
+                  _lib.ptr(entry["bias"]), UP.data_ptr(), DOWN.data_ptr(), C_packed.data_ptr(),
+                  OUT.data_ptr(), m, d, h, cf, flags, *_lib.workspace(dev), far.ptr_array,
+                  far.rank, far.world, far.block_bytes)
+    elif (route is not None and route["dense_all_tokens"] is not None
             and m >= route["dense_all_tokens"]):
         # so many tokens that every row is cheaper as dense GEMMs: no slab is produced
         ws_ptr, _ = _hybrid_workspace(dev, m, d, h, 0)
@@ -510,6 +517,18 @@ def set_d2t_layer_dense_route(layer_number: int, DOWN_T: torch.Tensor | None, *,
     entry["dense_route"] = {"DOWN_T": DOWN_T, "dense_cap": dense_cap,
                             "nnz_threshold": nnz_threshold, "min_tokens": int(min_tokens),
                             "dense_all_tokens": dense_all_tokens, "last": None}
+
+
+def set_d2t_layer_fused_allreduce(layer_number: int, fused) -> None:
+    """Extension for d_ff-sharded layers: ``fused`` is a
+    :class:`sparser_faster_llms_b200.peer_allreduce.FusedShardAllReduce` (or None to detach).
+    Gated calls it serves (decode-sized token counts) then return the sum over all ranks'
+    shards; every rank must make the same calls.  No reference counterpart."""
+    entry = _layer(layer_number)
+    if fused is None:
+        entry.pop("fused_allreduce", None)
+    else:
+        entry["fused_allreduce"] = fused
 
 
 def d2t_layer_dense_route_counters(layer_number: int) -> dict | None:

@@ -69,10 +69,38 @@ def _worker(rank, world, port, out_dir):
         torch.cuda.synchronize(dev)
         rel = ((ya.float() - yb.float()).norm() / yb.float().norm()).item()
         ok = ok and rel < 1e-2 and par.status() == 0
+        # contraction fused with the all-reduce: identical bits to contraction + peer all-reduce
+        # (same rounding points, same rank order), for the few-token multi-cluster shape
+        # (batch 1, 8) and the one-cluster shape (batch 32), repeated calls, graph replay
+        far = peer_allreduce.FusedShardAllReduce(32, d, device=dev)
+        c = sharded.ShardedTwELLGatedMLP(2, *args, fused_allreduce=far)
+        for m_f in (1, 8, 32, 8, 32):
+            xf = synthetic.make_tokens(m_f, d, seed=200 + m_f).to(dev)
+            yf, yp = c(xf), a(xf)
+            torch.cuda.synchronize(dev)
+            ok = ok and torch.equal(yf, yp)
+        xf = synthetic.make_tokens(32, d, seed=300).to(dev)
+        yp = a(xf).clone()
+        sg = torch.cuda.Stream(dev)
+        sg.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(sg):
+            c(xf)
+        torch.cuda.current_stream(dev).wait_stream(sg)
+        torch.cuda.synchronize(dev)
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=sg):
+            yg = c(xf)
+        for _ in range(4):
+            yg.zero_()
+            g2.replay()
+            torch.cuda.synchronize(dev)
+            ok = ok and torch.equal(yg, yp)
+        ok = ok and far.status() == 0 and par.status() == 0
         with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
             f.write(f"{int(ok)} {rel}")
         a.destroy()
         b.destroy()
+        c.destroy()
         torch.cuda.synchronize(dev)
         dist.barrier()
     finally:
