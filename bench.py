@@ -287,6 +287,10 @@ def run_ours(args):
     # Multi-rank steps are captured with their NCCL all-reduces inside the graph
     # (--eager-collectives launches them eagerly instead).
     graphed = not args.no_graph and (not dist_on or not args.eager_collectives)
+    if dist_on:
+        # the peer kernels wait (bounded) for one another: start the first step together
+        torch.cuda.synchronize(device)
+        dist.barrier()
     run_step = capture(step, device).replay if graphed else step
     ms_step = time_replays(run_step, args.steps, args.warmup, device, dist_on)
     clocks = sampler.stop() if rank == 0 else None
@@ -418,6 +422,9 @@ def run_e2e(args, layers, x, device, dist_on, par=None):
     else:
         mods = [twell.TwELLGatedMLP(1000 + l, g, u, dn, preallocate_shared_hidden_state=True)
                 for l, (g, u, dn) in enumerate(layers)]
+    if dist_on:
+        torch.cuda.synchronize(device)
+        dist.barrier()  # the warm-up steps inside the constructor exchange with the peers
     runner = stack.GraphedFFNStack(mods, B, return_last_only=True, device=device)
     runner.x_host.copy_(x.cpu())
     for _ in range(3):
