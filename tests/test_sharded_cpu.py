@@ -157,6 +157,46 @@ def test_sharded_training_forward_backward_equals_unsharded(tmp_path, world):
         assert np.allclose(o["dV"], V.grad.numpy()[h0:h1], rtol=1e-4, atol=1e-5)
 
 
+def test_fused_allreduce_is_attached_only_to_calls_it_serves():
+    """Host logic of the sharded module's fused path, with fakes: a call the fused form serves
+    attaches it to the layer's cached state and returns the local module's (already reduced)
+    output; any other call detaches it and goes through the separate all-reduce."""
+    from sparser_faster_llms_b200 import twell
+
+    class FakeLocal(nn.Module):
+        layer_number = 4711
+
+        def __init__(self, layer_number, GATE, UP, DOWN, **kw):
+            super().__init__()
+            twell._D2T_LAYERS[self.layer_number] = {"B": GATE, "cf": 8, "bias": None, "m": None}
+
+        def forward(self, A):
+            fused = "fused_allreduce" in twell._D2T_LAYERS[self.layer_number]
+            return A + (100.0 if fused else 1.0)
+
+    class FakeFused:
+        def serves(self, tokens, d_model):
+            return tokens <= 4
+
+    class FakePeer:
+        def all_reduce(self, y):
+            return y * 2
+
+    w = torch.zeros(512, 8)
+    mod = sharded.ShardedTwELLGatedMLP(0, w, w, w, rank=0, world_size=2, presharded=True,
+                                       local_factory=FakeLocal, fused_allreduce=FakeFused(),
+                                       peer_allreduce=FakePeer())
+    try:
+        small, large = torch.zeros(2, 2, 8), torch.zeros(3, 5, 8)   # 4 and 15 tokens
+        assert torch.equal(mod(small), small + 100.0)
+        assert "fused_allreduce" in twell._D2T_LAYERS[4711]
+        assert torch.equal(mod(large), (large + 1.0) * 2)
+        assert "fused_allreduce" not in twell._D2T_LAYERS[4711]
+        assert torch.equal(mod(small), small + 100.0)
+    finally:
+        twell._D2T_LAYERS.pop(4711, None)
+
+
 def _early_exit_worker(rank, world, port):
     import datetime
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
