@@ -67,11 +67,15 @@ class SparseDecoder(nn.Module):
     """``ffn`` = "twell" (this package's sparse path) or "dense" (cuBLAS)."""
 
     def __init__(self, cfg: DecoderConfig, batch: int, *, ffn: str = "twell", seed: int = 0,
-                 device="cuda"):
+                 device="cuda", shard: dict | None = None):
+        """``shard = {"rank", "world", "peer_allreduce", "fused_allreduce"}`` splits the d_ff of
+        every TwELL FFN over the ranks of a process group (attention, norms and the LM head stay
+        replicated); every rank then holds the same activations and generates the same tokens."""
         super().__init__()
         if ffn not in ("twell", "dense"):
             raise ValueError("ffn must be 'twell' or 'dense'")
         self.cfg, self.batch, self.kind = cfg, int(batch), ffn
+        self.shard = shard if (shard and shard.get("world", 1) > 1 and ffn == "twell") else None
         dev = torch.device(device)
         gen = torch.Generator().manual_seed(seed)
         bf = torch.bfloat16
@@ -91,6 +95,19 @@ class SparseDecoder(nn.Module):
         for l in range(cfg.layers):
             f = synthetic.make_ffn(d, cfg.d_ff, seed=seed * 1000 + l, density=cfg.density,
                                    skew_sigma=cfg.skew_sigma, fold_bias=False)
+            if self.shard is not None:
+                from . import sharded
+                r, w = self.shard["rank"], self.shard["world"]
+                h0, h1 = sharded.shard_range(cfg.d_ff, r, w)
+                gs, us, ds = (t[h0:h1].contiguous().to(dev) for t in (f.gate, f.up, f.down))
+                m = sharded.ShardedTwELLGatedMLP(
+                    7000 + l, gs, us, ds, rank=r, world_size=w, presharded=True,
+                    peer_allreduce=self.shard.get("peer_allreduce"),
+                    fused_allreduce=self.shard.get("fused_allreduce"),
+                    preallocate_shared_hidden_state=True)
+                m.local.set_gate_bias(f.gate_bias[h0:h1].to(dev))
+                self.ffns.append(m)
+                continue
             g, u, dn, b = f.gate.to(dev), f.up.to(dev), f.down.to(dev), f.gate_bias.to(dev)
             if ffn == "twell":
                 m = twell.TwELLGatedMLP(7000 + l, g, u, dn, preallocate_shared_hidden_state=True)
@@ -226,26 +243,40 @@ class SparseDecoder(nn.Module):
 
 
 def time_decode(cfg: DecoderConfig, batch: int, prompt: int, generate: int, ffn: str,
-                seed: int = 0, reps: int = 3) -> dict:
+                seed: int = 0, reps: int = 3, shard: dict | None = None) -> dict:
     """Prefill ``prompt`` random ids, then time ``generate`` graph-replayed decode steps with
-    CUDA events on the current stream; ``reps`` times from the same prompt, best and median."""
+    CUDA events on the current stream; ``reps`` times from the same prompt, best and median.
+    With ``shard`` (several ranks) every run starts behind a barrier and the time is the
+    maximum over ranks."""
+    import torch.distributed as dist
     dev = torch.device("cuda", torch.cuda.current_device())
-    model = SparseDecoder(cfg, batch, ffn=ffn, seed=seed, device=dev)
+    model = SparseDecoder(cfg, batch, ffn=ffn, seed=seed, device=dev, shard=shard)
+    multi = model.shard is not None
     ids = torch.randint(0, cfg.vocab, (batch, prompt), generator=torch.Generator().manual_seed(7))
     ids = ids.to(dev)
     runs = []
     for _ in range(reps):
+        if multi:
+            torch.cuda.synchronize(dev)
+            dist.barrier()
         model.prefill(ids)
         if model.graph is None:
             model.capture()
         model.generate(8)                      # warm-up replays
         torch.cuda.synchronize(dev)
+        if multi:
+            dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         toks = model.generate(generate - 8)
         e1.record()
         torch.cuda.synchronize(dev)
-        runs.append(e0.elapsed_time(e1) / (generate - 8))
+        ms_run = e0.elapsed_time(e1) / (generate - 8)
+        if multi:
+            t = torch.tensor([ms_run], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_run = float(t.item())
+        runs.append(ms_run)
     ms = min(runs)
     out = {"ffn": ffn, "ms_per_token": ms, "ms_per_token_median": sorted(runs)[len(runs) // 2],
            "tokens_per_s": batch / (ms * 1e-3),
@@ -270,16 +301,47 @@ def main() -> None:
     ap.add_argument("--generate", type=int, default=256)
     ap.add_argument("--layers", type=int, default=28)
     args = ap.parse_args()
+    import os
+    import sys
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     cfg = DecoderConfig(layers=args.layers,
                         max_seq=int(math.ceil((args.prompt + args.generate + 8) / 128) * 128))
-    for b in [int(s) for s in args.batch.split(",")]:
-        rec = {"batch": b, "prompt": args.prompt, "generate": args.generate, "layers": cfg.layers,
-               "d_model": cfg.d_model, "d_ff": cfg.d_ff, "heads": cfg.heads, "vocab": cfg.vocab,
-               "gate_density": cfg.density, "dtype": "bf16", "data": "synthetic"}
-        for kind in ("twell", "dense"):
-            rec[kind] = time_decode(cfg, b, args.prompt, args.generate, kind)
-        rec["speedup_vs_dense_ffn"] = rec["dense"]["ms_per_token"] / rec["twell"]["ms_per_token"]
-        print(json.dumps(rec), flush=True)
+    batches = [int(s) for s in args.batch.split(",")]
+    shard = None
+    if world > 1:
+        # torchrun: the TwELL FFN is d_ff-sharded over the ranks, the shard sum runs inside the
+        # contraction kernel for decode steps and through the peer all-reduce / NCCL for prefill
+        from . import peer_allreduce
+        shard = {"rank": rank, "world": world,
+                 "peer_allreduce": peer_allreduce.PeerAllReduce(max(batches) * cfg.d_model * 2,
+                                                                device=dev),
+                 "fused_allreduce": peer_allreduce.FusedShardAllReduce(max(batches), cfg.d_model,
+                                                                       device=dev)}
+    for b in batches:
+        rec = {"batch": b, "n_gpus": world, "prompt": args.prompt, "generate": args.generate,
+               "layers": cfg.layers, "d_model": cfg.d_model, "d_ff": cfg.d_ff, "heads": cfg.heads,
+               "vocab": cfg.vocab, "gate_density": cfg.density, "dtype": "bf16",
+               "data": "synthetic"}
+        rec["twell"] = time_decode(cfg, b, args.prompt, args.generate, "twell", shard=shard)
+        if rank == 0:  # the comparison point is the unsharded dense-FFN model on one GPU
+            rec["dense"] = time_decode(cfg, b, args.prompt, args.generate, "dense")
+            rec["speedup_vs_dense_ffn"] = rec["dense"]["ms_per_token"] / rec["twell"]["ms_per_token"]
+            if shard is not None:
+                rec["allreduce_status"] = [shard["peer_allreduce"].status(),
+                                           shard["fused_allreduce"].status()]
+            print(json.dumps(rec), flush=True)
+        if world > 1:
+            torch.cuda.synchronize(dev)
+            dist.barrier()
+    if world > 1:
+        sys.stdout.flush()
+        os._exit(0)  # captured graphs hold communicator state: skip the collective teardown
 
 
 if __name__ == "__main__":

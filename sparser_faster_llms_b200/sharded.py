@@ -172,8 +172,10 @@ class ShardedTwELLGatedMLP(nn.Module):
             if entry is not None:
                 entry.pop("fused_allreduce", None)  # a call the fused form does not serve
         y = self.local(A)
-        if self.world_size > 1 and self.peer_allreduce is not None:
-            return self.peer_allreduce.all_reduce(y.contiguous())
+        par = self.peer_allreduce
+        if (self.world_size > 1 and par is not None
+                and y.numel() * y.element_size() <= getattr(par, "max_bytes", float("inf"))):
+            return par.all_reduce(y.contiguous())  # larger outputs (prefill) go through NCCL
         if self.world_size > 1:
             if self.reduce_dtype is not None and self.reduce_dtype != y.dtype:
                 acc = y.to(self.reduce_dtype)
