@@ -40,14 +40,18 @@ int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, con
                      void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream,
                      const unsigned char* skip_rows = nullptr, const FusedAr* fused_ar = nullptr);
 
-bool pdl_enabled() {
-  static int state = -1;
-  if (state < 0) {
+int pdl_mask() {
+  static int mask = -1;
+  if (mask < 0) {
     const char* e = getenv("B200_PDL");
-    state = (e != nullptr) ? (e[0] != '0') : B200_PDL_DEFAULT;
+    int v = (e != nullptr) ? atoi(e) : B200_PDL_DEFAULT;
+    if (v == 1) v = 3;
+    mask = v & 3;
   }
-  return state != 0;
+  return mask;
 }
+
+bool pdl_enabled() { return pdl_mask() != 0; }
 
 // Number of SMs of the current device (cached per device ordinal).
 int sm_count() {

@@ -79,9 +79,15 @@ inline bool& pdl_suppressed() {
   return suppressed;
 }
 
-// Appends the attribute to attrs[n] when enabled; returns the new count.
-inline unsigned add_pdl_attribute(cudaLaunchAttribute* attrs, unsigned n) {
-  if (!pdl_enabled() || pdl_suppressed()) return n;
+// Which launches take the attribute: bit 0 the pack kernels (successors of a contraction),
+// bit 1 the contraction kernel (successor of a pack kernel).  B200_PDL = 1 or 3 sets both,
+// 2 only the contraction.
+int pdl_mask();
+
+// Appends the attribute to attrs[n] when enabled for this kind of launch (1 pack,
+// 2 contraction); returns the new count.
+inline unsigned add_pdl_attribute(cudaLaunchAttribute* attrs, unsigned n, int kind = 3) {
+  if (!pdl_enabled() || pdl_suppressed() || !(pdl_mask() & kind)) return n;
   attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attrs[n].val.programmaticStreamSerializationAllowed = 1;
   return n + 1;

@@ -253,7 +253,7 @@ int launch_pack(const void* x, const void* w, const float* bias, void* packed, i
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = add_pdl_attribute(attr, 1);
+  cfg.numAttrs = add_pdl_attribute(attr, 1, 1);
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, reinterpret_cast<const __nv_bfloat16*>(x),
                                      reinterpret_cast<const __nv_bfloat16*>(w), bias,
                                      reinterpret_cast<uint32_t*>(packed), (int)M, (int)D, slab_w,

@@ -437,7 +437,7 @@ int launch_tc_splitk(const void* x, const void* w, const float* bias, void* pack
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = add_pdl_attribute(attr, 1);
+  cfg.numAttrs = add_pdl_attribute(attr, 1, 1);
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, bias,
                                      static_cast<uint32_t*>(packed), (int)M, (int)D, slab_w,
                                      tiles * slab_w);

@@ -446,7 +446,7 @@ int launch_t2d(const void* x, const void* packed, const void* up, const void* do
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = add_pdl_attribute(attr, 1);
+  cfg.numAttrs = add_pdl_attribute(attr, 1, 2);
   cudaError_t e = cudaLaunchKernelEx(
       &cfg, kern, reinterpret_cast<const __nv_bfloat16*>(x),
       reinterpret_cast<const uint32_t*>(packed), reinterpret_cast<const __nv_bfloat16*>(up),
