@@ -26,7 +26,7 @@ class GraphedFFNStack:
     """
 
     def __init__(self, mlps, batch: int, *, return_last_only: bool = False,
-                 device: torch.device | str | None = None, copy_chunk: int = 2):
+                 device: torch.device | str | None = None, copy_chunk: int = 4):
         self.mlps = list(mlps)
         if not self.mlps:
             raise ValueError("need at least one module")
@@ -55,19 +55,21 @@ class GraphedFFNStack:
         # The host -> device copies run on a second stream in chunks of a few layers, each
         # chunk followed by an event the compute stream waits on: layer l starts as soon as
         # its own input has arrived, and the rest of the transfer hides under the kernels.
+        # The first chunk is a single layer, so the compute stream starts after one small copy.
         main = torch.cuda.current_stream(self.device)
         self.copy_stream.wait_stream(main)
-        ready = []
+        bounds = [0, 1] + list(range(1 + self.copy_chunk, self.layers, self.copy_chunk))
+        bounds = [b for b in bounds if b < self.layers] + [self.layers]
+        ready = {}
         with torch.cuda.stream(self.copy_stream):
-            for l0 in range(0, self.layers, self.copy_chunk):
-                l1 = min(self.layers, l0 + self.copy_chunk)
+            for l0, l1 in zip(bounds[:-1], bounds[1:]):
                 self.x_dev[l0:l1].copy_(self.x_host[l0:l1], non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(self.copy_stream)
-                ready.append(ev)
+                ready[l0] = ev
         for l, mlp in enumerate(self.mlps):
-            if l % self.copy_chunk == 0:
-                main.wait_event(ready[l // self.copy_chunk])
+            if l in ready:
+                main.wait_event(ready[l])
             y = mlp(self.x_dev[l])
             # only what is returned is gathered: with return_last_only the last layer's
             # output goes to the host straight from the module's own tensor
