@@ -29,6 +29,8 @@
 // barrier / counter that precedes the first store.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -492,7 +494,12 @@ void t2d_shape(int64_t M, int64_t D, int sm_count, size_t workspace_bytes, int* 
   if (workspace_bytes > kCounterWords * 4 && M * 8 <= (int64_t)kCounterWords) {
     const int64_t cap_floats = (int64_t)((workspace_bytes - kCounterWords * 4) / 4);
     int64_t want = ((int64_t)sm_count * 2) / (M * cs);  // about two CTAs per SM in total
-    if (want > 32) want = 32;
+    static const int max_nc = [] {  // tuning knob: B200_T2D_MAX_NC caps the clusters per token
+      const char* e = getenv("B200_T2D_MAX_NC");
+      const int v = e != nullptr ? atoi(e) : 32;
+      return v >= 1 && v <= 32 ? v : 32;
+    }();
+    if (want > max_nc) want = max_nc;
     while (want > 1 && M * want * D > cap_floats) --want;
     if (want > 1) nc = (int)want;
   }
