@@ -215,6 +215,20 @@ int b200_hybrid_wgrad_dense(const void* vals_slab, const void* rows, void* out, 
                             size_t ws_bytes, void* stream);
 
 /*
+ * Dead-neuron bookkeeping for the hybrid path.  active_rows[j] (int32 [H], overwritten) =
+ * number of token rows whose stored value for neuron j is non-zero; the values are read
+ * from vals_slab (the forward's T = relu(gate)*up slab), or from p_slab itself when
+ * vals_slab is NULL.  When last_activated (int64 [H]) is not NULL it is updated in place:
+ * 0 for a neuron with active_rows > 0, else + microbatch_tokens.  Entries a slab dropped on
+ * overflow are not seen.  Supplies what SparsityTracker.record_activations computes from the
+ * dense activation (custom_models/sparse_models.py:148-181) and record_l0_l1 leaves stale
+ * on the fused path (:183-208).
+ */
+int b200_hybrid_neuron_activity(const void* p_slab, const void* vals_slab, int64_t M, int64_t H,
+                                int cf, int64_t microbatch_tokens, int* active_rows,
+                                int64_t* last_activated, void* stream);
+
+/*
  * Row-ELL x dense: C[r,:] = sum_k vals[r,k] * B[cols[r,k],:] for rows with
  * 0 < row_counts[r] <= overflow_threshold, zeros otherwise.  vals bf16 / cols uint16
  * [M, ell_stride], B [K, N] bf16, C [M, N] bf16.  Replaces ell_spmm_raw

@@ -220,6 +220,34 @@ def l0_l1(h_abs: torch.Tensor):
     return l0, l1
 
 
+def last_activated_update(h_abs: torch.Tensor, last_activated: torch.Tensor,
+                          microbatch_tokens: int):
+    """Dead-neuron counter update from the dense activation (sparse_models.py:170-181):
+    a neuron active for any token restarts at 0, the others age by ``microbatch_tokens``.
+    Returns ``(active_rows int32 [H], new last_activated int64 [H])``."""
+    h_abs = h_abs.reshape(-1, h_abs.shape[-1])
+    active_rows = (h_abs > 0).sum(0).to(torch.int32)
+    new = torch.where(active_rows > 0, torch.zeros_like(last_activated),
+                      last_activated + int(microbatch_tokens))
+    return active_rows, new
+
+
+def slab_active_rows(p_slab: np.ndarray, vals_slab: np.ndarray | None, output_n: int,
+                     compression_factor: int = 8) -> np.ndarray:
+    """Per-neuron count of rows whose stored value is not +-0, read from slab arrays (the
+    pattern ``p_slab`` gives the columns, ``vals_slab`` the values when given).  Entries a
+    slab dropped on overflow are not seen, as on the device."""
+    w = tf.slab_words(compression_factor)
+    tiles = output_n // TILE_N
+    p = np.ascontiguousarray(p_slab).view(np.uint32).reshape(-1, tiles, w)
+    v = p if vals_slab is None else np.ascontiguousarray(vals_slab).view(np.uint32).reshape(p.shape)
+    cnt = np.clip(p[:, :, 0].astype(np.int64), 0, w - 1)
+    stored = np.arange(1, w)[None, None, :] <= cnt[:, :, None]
+    nonzero = ((v[:, :, 1:] >> 16) & 0x7FFF) != 0
+    cols = (p[:, :, 1:] & 0xFFFF)[stored & nonzero]
+    return np.bincount(cols, minlength=output_n).astype(np.int32)
+
+
 # --------------------------------------------------------------------------
 # error metrics
 # --------------------------------------------------------------------------

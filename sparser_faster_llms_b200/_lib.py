@@ -57,6 +57,9 @@ _PROTOTYPES = {
     "b200_hybrid_wgrad_dense": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                         c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "b200_hybrid_ell_spmm_raw": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_void_p]),
+    # p_slab, vals_slab, M, H, cf, microbatch_tokens, active_rows, last_activated, stream
+    "b200_hybrid_neuron_activity": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64,
+                                            c_void_p, c_void_p, c_void_p]),
     "b200_twell_hybrid_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),
     # x, packed, gate, gate_bias, up, down, down_t, out, M, D, H, cf, flags, nnz_threshold,
     # dense_cap, hybrid_ws, hybrid_ws_bytes, workspace, workspace_bytes, stream

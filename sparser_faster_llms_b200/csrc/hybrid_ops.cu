@@ -215,6 +215,34 @@ __global__ void hyb_fill_kernel(const uint32_t* __restrict__ P, int M, int tiles
   }
 }
 
+// ---- per-neuron activity (dead-neuron bookkeeping) ---------------------------
+// The reference tracker marks a neuron active in a micro-batch when |h| > 0 for some token
+// (SparsityTracker.record_activations, custom_models/sparse_models.py:148-181) but cannot
+// do so on the hybrid path, which never materialises h (record_l0_l1, :183-208).  Here h
+// is the slab T of the forward, so the mask costs one pass over P and T: one warp per
+// (row, tile) slab counts, per neuron, the rows whose stored value is not +-0.
+__global__ void hyb_activity_count_kernel(const uint32_t* __restrict__ P,
+                                          const uint32_t* __restrict__ vals, int M, int tiles,
+                                          int W, int* __restrict__ active_rows) {
+  const int64_t slab = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (slab >= (int64_t)M * tiles) return;
+  const int lane = threadIdx.x & 31;
+  const uint32_t* s = P + slab * W;
+  const uint32_t* v = vals != nullptr ? vals + slab * W : s;
+  const int cnt = min(max((int)s[0], 0), W - 1);
+  for (int i = lane; i < cnt; i += 32) {
+    if (((v[1 + i] >> 16) & 0x7FFFu) != 0u) atomicAdd(&active_rows[s[1 + i] & 0xFFFFu], 1);
+  }
+}
+
+// last_activated[j] = 0 for a neuron seen active, else + microbatch_tokens (:175-181).
+__global__ void hyb_activity_update_kernel(const int* __restrict__ active_rows,
+                                           long long* __restrict__ last_activated,
+                                           long long microbatch_tokens, int H) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j < H) last_activated[j] = active_rows[j] > 0 ? 0ll : last_activated[j] + microbatch_tokens;
+}
+
 // ---- transposed products ----------------------------------------------------
 // One cluster of kSplitT CTAs per column j, one warp per 256-column slice of D.  The
 // cluster's CTAs take the column's entry batches round-robin (a hot neuron's long list
@@ -455,6 +483,36 @@ int b200_hybrid_csc_build(const void* p_slab, int* col_count, int* col_start, in
                                             overflow);
   } else {
     hyb_scan_kernel<<<1, 1024, 0, st>>>(col_count, col_start, cursor, (int)H);
+  }
+  return check_launch(fn);
+}
+
+int b200_hybrid_neuron_activity(const void* p_slab, const void* vals_slab, int64_t M, int64_t H,
+                                int cf, int64_t microbatch_tokens, int* active_rows,
+                                int64_t* last_activated, void* stream) {
+  const char* fn = "b200_hybrid_neuron_activity";
+  if (M < 0 || H <= 0 || H % kTileN || H > 65536)
+    return fail(B200_EUNSUPPORTED, "%s: H must be a multiple of 256, at most 65536", fn);
+  if (cf != 2 && cf != 4 && cf != 8) return fail(B200_EUNSUPPORTED, "%s: cf must be 2, 4 or 8", fn);
+  if (microbatch_tokens < 0) return fail(B200_EINVAL, "%s: microbatch_tokens is negative", fn);
+  if (active_rows == nullptr) return fail(B200_ENULL, "%s: active_rows is NULL", fn);
+  if (M > 0 && p_slab == nullptr) return fail(B200_ENULL, "%s: p_slab is NULL", fn);
+  if ((int64_t)M * (H / kTileN) * (kTileN / cf) > 0x7fffffffLL)
+    return fail(B200_EUNSUPPORTED, "%s: slab array exceeds 2^31 words", fn);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(active_rows, 0, sizeof(int) * (size_t)H, st);
+  if (e != cudaSuccess) return fail(B200_ECUDA, "%s: memset: %s", fn, cudaGetErrorString(e));
+  const int tiles = (int)(H / kTileN), W = kTileN / cf;
+  if (M > 0) {
+    const int64_t slabs = M * tiles;
+    hyb_activity_count_kernel<<<(unsigned)((slabs + 7) / 8), 256, 0, st>>>(
+        static_cast<const uint32_t*>(p_slab), static_cast<const uint32_t*>(vals_slab), (int)M,
+        tiles, W, active_rows);
+  }
+  if (last_activated != nullptr) {
+    hyb_activity_update_kernel<<<(unsigned)((H + 255) / 256), 256, 0, st>>>(
+        active_rows, reinterpret_cast<long long*>(last_activated), (long long)microbatch_tokens,
+        (int)H);
   }
   return check_launch(fn);
 }

@@ -415,6 +415,45 @@ def reset_stats() -> None:
     _PERF.clear()
 
 
+def neuron_activity(P, T=None, last_activated: torch.Tensor | None = None,
+                    microbatch_tokens: int = 0, width: int | None = None) -> torch.Tensor:
+    """Per-neuron activity of one forward: ``active_rows`` int32 ``[H]`` = number of tokens
+    with a non-zero stored value for the neuron (values from ``T``, the forward's
+    ``relu(gate)*up`` slab, else from the pattern ``P``).  With ``last_activated`` (int64
+    ``[H]``, updated in place) active neurons restart at 0 and the others age by
+    ``microbatch_tokens``: the update SparsityTracker.record_activations applies from the
+    dense activation (custom_models/sparse_models.py:170-181), which the reference's fused
+    path leaves stale (:183-208).  ``P`` / ``T`` are the int32 slab tensors the forward
+    returns, or :class:`HybridSp` wrappers."""
+    if isinstance(P, HybridSp):
+        width = P.n if width is None else width
+        cf, P = P.cf, P.slab
+    else:
+        cf = compression_factor()
+    if isinstance(T, HybridSp):
+        T = T.slab
+    if width is None:
+        width = P.shape[1] // (TILE // cf) * TILE
+    if not P.is_cuda:
+        raise RuntimeError("P must be a CUDA tensor: sparse_ops has no CPU implementation")
+    m = P.shape[0]
+    if tuple(P.shape) != _slab_shape(m, width, cf):
+        raise ValueError(f"P {tuple(P.shape)} is not a slab array of width {width} at cf {cf}")
+    if T is not None and (T.shape != P.shape or T.device != P.device):
+        raise ValueError("T must have P's shape and device")
+    dev = P.device
+    if last_activated is not None:
+        if (last_activated.dtype != torch.int64 or last_activated.shape != (width,)
+                or last_activated.device != dev or not last_activated.is_contiguous()):
+            raise ValueError(f"last_activated must be a contiguous int64 [{width}] tensor on {dev}")
+    active_rows = torch.empty(width, dtype=torch.int32, device=dev)
+    P = P.contiguous()
+    T = None if T is None else T.contiguous()
+    _lib.call("b200_hybrid_neuron_activity", dev, P.data_ptr(), _lib.ptr(T), m, width, cf,
+              int(microbatch_tokens), active_rows.data_ptr(), _lib.ptr(last_activated))
+    return active_rows
+
+
 def ff_forward_gated(X, G, K, V):
     """Direct (non-dispatcher) forward returning :class:`HybridSp` objects like the
     reference's CUDA implementation (custom_op.cpp:40-137)."""

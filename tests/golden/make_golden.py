@@ -223,17 +223,69 @@ def case_state_dicts(reference_root: str, out: Path):
     (out / "state_dict_conversions.json").write_text(json.dumps(golden, indent=1, sort_keys=True))
 
 
+TRACKER_ARGS = dict(train_batch_size=8, max_seq_len=16, per_device_train_batch_size=2,
+                    tokens_until_dead=96, gated=True)
+
+
+def tracker_inputs():
+    """Seeded ``|h|`` micro-batches ``[step][layer] -> [2, 16, 512]`` fp32 for the tracker
+    case: ~3 % dense, with neurons 0..63 of layer 0 never firing and neurons 64..127 firing
+    only in step 0, so some counters cross ``tokens_until_dead``."""
+    gen = torch.Generator().manual_seed(77)
+    steps = []
+    for step in range(5):
+        layers = []
+        for layer in range(2):
+            h = torch.rand(2, 16, 512, generator=gen)
+            h = torch.where(torch.rand(2, 16, 512, generator=gen) < 0.03, h, torch.zeros(()))
+            if layer == 0:
+                h[..., :64] = 0
+                if step > 0:
+                    h[..., 64:128] = 0
+            layers.append(h)
+        steps.append(layers)
+    return steps
+
+
+def case_tracker(ref, out: Path):
+    """The reference's SparsityTracker (custom_models/sparse_models.py:95-256) driven over
+    ``tracker_inputs()`` through record_activations: per step the ``_last_activated``
+    counters, alive masks, L1 loss and logged statistics."""
+    import contextlib
+    import io
+    import json
+    with contextlib.redirect_stdout(io.StringIO()):
+        tr = ref.SparsityTracker(**TRACKER_ARGS)
+    golden = []
+    for layers in tracker_inputs():
+        tr.start_forward_pass()
+        for i, h in enumerate(layers):
+            tr.record_activations(layer_idx=i, absolute_activations=h)
+        l1, stats = tr.finalize_forward_pass()
+        golden.append({
+            "l1": float(l1),
+            "stats": {k: float(v) for k, v in stats.items()},
+            "last_activated": [tr._last_activated[i].tolist() for i in range(len(layers))],
+            "alive": [int(a.sum()) for a in tr.get_alive_neurons()],
+        })
+    (out / "sparsity_tracker.json").write_text(json.dumps(golden, sort_keys=True))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=str(REPO.parent / "reference"),
                     help="checkout of the reference (default: a sibling of this repository)")
     ap.add_argument("--only-state-dicts", action="store_true")
+    ap.add_argument("--only-tracker", action="store_true")
     args = ap.parse_args()
     if args.only_state_dicts:
         case_state_dicts(args.reference, HERE)
         return
     sys.path.insert(0, args.reference)
     from custom_models import sparse_models as ref
+    if args.only_tracker:
+        case_tracker(ref, HERE)
+        return
     import importlib.util
     # twell.py imports torch.utils.cpp_extension only; it is safe to import on CPU.
     spec = importlib.util.spec_from_file_location(
@@ -245,6 +297,7 @@ def main():
     case_small(ref, twell_ref, HERE)
     case_training(ref, HERE)
     case_config1(ref, HERE)
+    case_tracker(ref, HERE)
     for p in sorted(HERE.glob("*.npz")):
         print(p.name, p.stat().st_size)
 

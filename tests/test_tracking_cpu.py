@@ -1,0 +1,109 @@
+"""Sparsity bookkeeping on CPU: the tracker mirror against vectors generated from the
+reference's SparsityTracker (custom_models/sparse_models.py:95-256; generator:
+tests/golden/make_golden.py --only-tracker), and the oracle's slab-level activity count
+against the dense definition."""
+import importlib.util
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ffn_oracle as fo
+from oracle import twell_format as tf
+from sparser_faster_llms_b200 import tracking
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def _generator():
+    spec = importlib.util.spec_from_file_location("make_golden", GOLDEN / "make_golden.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    return gen
+
+
+def test_tracker_reproduces_the_reference_vectors(monkeypatch):
+    monkeypatch.delenv("WORLD_SIZE", raising=False)
+    gen = _generator()
+    golden = json.loads((GOLDEN / "sparsity_tracker.json").read_text())
+    tr = tracking.SparsityTracker(**gen.TRACKER_ARGS)
+    shadow = None
+    for layers, want in zip(gen.tracker_inputs(), golden, strict=True):
+        if shadow is None:
+            shadow = [torch.zeros(h.shape[-1], dtype=torch.int64) for h in layers]
+        tr.start_forward_pass()
+        for i, h in enumerate(layers):
+            tr.record_activations(layer_idx=i, absolute_activations=h)
+            _, shadow[i] = fo.last_activated_update(h, shadow[i], tr._microbatch_tokens)
+        l1, stats = tr.finalize_forward_pass()
+        assert float(l1) == pytest.approx(want["l1"], rel=1e-6)
+        assert {k: float(v) for k, v in stats.items()} == pytest.approx(want["stats"], rel=1e-6)
+        for i in range(len(layers)):
+            assert tr._last_activated[i].tolist() == want["last_activated"][i]
+            assert shadow[i].tolist() == want["last_activated"][i]  # the oracle agrees too
+        assert [int(a.sum()) for a in tr.get_alive_neurons()] == want["alive"]
+
+
+def test_tracker_gating_rules():
+    tr = tracking.SparsityTracker(4, 8, 1, total_devices=2)
+    assert (tr._batch_tokens, tr._microbatch_tokens, tr._tokens_until_dead) == (16, 8, 16)
+    with pytest.raises(ValueError, match="finalize_forward_pass"):
+        tr.get_alive_neurons()
+    h = torch.rand(1, 8, 256)
+    tr.record_activations(0, h)                 # inactive, grad enabled: ignored
+    assert tr._l1_per_layer == [] and 0 not in tr._last_activated
+    with torch.no_grad():
+        tr.record_activations(0, h)             # inactive, no grad: L1 only
+    assert len(tr._l1_per_layer) == 1 and tr._l0_per_layer == []
+    assert int(tr._last_activated[0].sum()) == 0
+    l1, stats = tr.finalize_forward_pass()
+    assert stats == {} and float(l1) == pytest.approx(float(h.sum(-1).mean()))
+    assert tracking.SparsityTracker(4, 8, 1).finalize_forward_pass() == (0.0, {})
+    null = tracking.NullTracker(4, 8)
+    null.record_pattern(0, None, None, None)
+    assert null.finalize_forward_pass()[1] == {}
+
+
+def test_record_l0_l1_leaves_counters_stale_like_the_reference():
+    tr = tracking.SparsityTracker(4, 8, 1)
+    tr.start_forward_pass()
+    tr.record_l0_l1(0, torch.tensor(3.0), torch.tensor(0.5), width=256)
+    assert tr._last_activated[0].shape == (256,) and int(tr._last_activated[0].sum()) == 0
+    _, stats = tr.finalize_forward_pass()
+    assert float(stats["activation_l0/mean"]) == 3.0
+
+
+def test_select_fast_layers():
+    l0 = [torch.tensor(10.0), torch.tensor(200.0), 99.9]
+    assert tracking.select_fast_layers(l0, 100) == [True, False, True]
+    assert tracking.select_fast_layers(l0, -1) == [True, True, True]
+
+
+@pytest.mark.parametrize("cf", [8, 4])
+def test_slab_activity_matches_the_dense_definition(cf):
+    rng = np.random.default_rng(5)
+    m, h = 37, 768
+    z = rng.standard_normal((m, h)).astype(np.float32)
+    z[rng.random((m, h)) > 0.05] = -1.0          # ~5 % positive: no slab overflows
+    z[:, 10:20] = -1.0
+    packed = tf.pack_preactivations(z, cf)
+    dense = tf.unpack_to_dense(packed, h, cf)
+    want = (dense > 0).sum(0).astype(np.int32)
+    got = fo.slab_active_rows(packed, None, h, cf)
+    assert np.array_equal(got, want) and got[10:20].sum() == 0
+    # a values slab with zeros in some stored entries: those entries stop counting
+    vals = packed.copy().reshape(m, h // 256, 256 // cf)
+    vals[:, :, 1::2] &= 0xFFFF                   # odd slots: value bits cleared (+0)
+    vals[:, :, 2::4] = (vals[:, :, 2::4] & 0xFFFF) | (0x8000 << 16)   # -0 is zero as well
+    p3 = packed.reshape(vals.shape)
+    cnt = np.clip(p3[:, :, 0].astype(np.int64), 0, 256 // cf - 1)
+    want2 = np.zeros(h, dtype=np.int32)
+    for r in range(m):
+        for t in range(h // 256):
+            for s in range(1, cnt[r, t] + 1):
+                if s % 2 == 0 and s % 4 != 2:
+                    want2[p3[r, t, s] & 0xFFFF] += 1
+    got2 = fo.slab_active_rows(packed, vals.reshape(packed.shape), h, cf)
+    assert np.array_equal(got2, want2)
