@@ -56,6 +56,10 @@ def parse():
     ap.add_argument("--d-ff", type=int, default=D_FF)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-energy", action="store_true",
+                    help="skip the energy-per-step measurement (single GPU only)")
+    ap.add_argument("--energy-seconds", type=float, default=1.5,
+                    help="length of each energy window (sparse stack, dense stack)")
     ap.add_argument("--eager-collectives", action="store_true",
                     help="multi-rank: launch the step eagerly instead of as one CUDA graph")
     ap.add_argument("--collective", default="fused", choices=["fused", "peer", "nccl"],
@@ -307,6 +311,26 @@ def run_ours(args):
         run_dense = dense_step if args.no_graph else capture(dense_step, device).replay
         ms_dense = time_replays(run_dense, max(10, args.steps // 2), 3, device, False)
 
+    # energy per step (the reference benchmark's --measure-energy figure, energy per forward:
+    # benchmark_inference.py:280-343), after the timed region, sparse and dense stacks alike
+    energy_row = None
+    if not dist_on and not args.no_energy:
+        try:
+            from sparser_faster_llms_b200 import energy as energy_mod
+            e_s = energy_mod.measure_replays(run_step, device, min_seconds=args.energy_seconds)
+            e_d = energy_mod.measure_replays(run_dense, device, min_seconds=args.energy_seconds)
+            if e_s is not None:
+                energy_row = {"j_per_step": e_s["energy_per_forward_j"],
+                              "j_per_token": e_s["energy_per_forward_j"] / B,
+                              "avg_power_w": e_s["avg_power_w"], "steps": e_s["reps"],
+                              "window_s": e_s["energy_duration_s"],
+                              "backend": e_s["energy_backend"]}
+                if e_d is not None:
+                    energy_row["dense_cublas_bf16_j_per_step"] = e_d["energy_per_forward_j"]
+                    energy_row["dense_cublas_bf16_avg_power_w"] = e_d["avg_power_w"]
+        except Exception as exc:  # a power query must never cost the benchmark line
+            energy_row = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+
     # dominant kernel alone (per-launch time, CUDA events on the launching stream)
     run_pack = pack_only if args.no_graph else capture(pack_only, device).replay
     ms_pack = time_replays(run_pack, max(10, args.steps // 2), 3, device, False) / L
@@ -355,6 +379,7 @@ def run_ours(args):
                      "us_per_launch": ms_pack * 1e3, "algorithmic_bytes": pack_bytes},
         "gpu_launches": args.steps * L * (3 if (par is not None and far is None) else 2),
         "clocks": clocks,
+        "energy": energy_row,
     }
 
     # the other decode batch sizes of the configuration, measured the same way (shorter)
