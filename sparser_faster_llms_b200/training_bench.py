@@ -101,6 +101,13 @@ def main() -> None:
         t_fb = _time(step, args.reps, args.warmup, dev)
         res[name] = {"forward_ms": t_f, "forward_backward_ms": t_fb, "backward_ms": t_fb - t_f}
     _, l0 = sparse_forward()
+    # dead-neuron bookkeeping of this rank's neuron shard (shard-local: no exchange needed)
+    with torch.no_grad():
+        _, _, _, p_slab, _, t_slab = torch.ops.sparse_ops.ff_forward_gated(x.detach(), g, k, v)
+        last = torch.zeros(g.shape[0], dtype=torch.int64, device=dev)
+        res["sparse"]["dead_neuron_bookkeeping_ms"] = _time(
+            lambda: sparse_ops.neuron_activity(p_slab, t_slab, last, b * s),
+            args.reps, args.warmup, dev)
     if world > 1:
         t = torch.tensor([res["sparse"]["forward_ms"], res["sparse"]["forward_backward_ms"]],
                          device=dev)

@@ -41,6 +41,17 @@ def test_sweep_bench_small():
             assert r["overflowed_rows"] > 0
 
 
+def test_training_bench_small():
+    recs = run_module("sparser_faster_llms_b200.training_bench", "--batch", "2", "--seq", "256",
+                      "--d-model", "512", "--d-ff", "1024", "--density", "0.03", "--reps", "2",
+                      "--warmup", "1")
+    assert len(recs) == 1
+    r = recs[0]
+    assert r["tokens"] == 512 and r["l0_per_token"] > 0
+    assert r["sparse"]["forward_backward_ms"] > r["sparse"]["forward_ms"] > 0
+    assert r["sparse"]["dead_neuron_bookkeeping_ms"] > 0 and r["dense"]["forward_ms"] > 0
+
+
 def test_decode_model_cli_small():
     recs = run_module("sparser_faster_llms_b200.decode_model", "--batch", "2", "--prompt", "32",
                       "--generate", "24", "--layers", "2")
