@@ -219,20 +219,45 @@ __global__ void hyb_fill_kernel(const uint32_t* __restrict__ P, int M, int tiles
 // The reference tracker marks a neuron active in a micro-batch when |h| > 0 for some token
 // (SparsityTracker.record_activations, custom_models/sparse_models.py:148-181) but cannot
 // do so on the hybrid path, which never materialises h (record_l0_l1, :183-208).  Here h
-// is the slab T of the forward, so the mask costs one pass over P and T: one warp per
-// (row, tile) slab counts, per neuron, the rows whose stored value is not +-0.
-__global__ void hyb_activity_count_kernel(const uint32_t* __restrict__ P,
-                                          const uint32_t* __restrict__ vals, int M, int tiles,
-                                          int W, int* __restrict__ active_rows) {
-  const int64_t slab = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (slab >= (int64_t)M * tiles) return;
-  const int lane = threadIdx.x & 31;
-  const uint32_t* s = P + slab * W;
-  const uint32_t* v = vals != nullptr ? vals + slab * W : s;
-  const int cnt = min(max((int)s[0], 0), W - 1);
-  for (int i = lane; i < cnt; i += 32) {
-    if (((v[1 + i] >> 16) & 0x7FFFu) != 0u) atomicAdd(&active_rows[s[1 + i] & 0xFFFFu], 1);
+// is the slab T of the forward, so the mask costs one pass over P and T, counting per neuron
+// the rows whose stored value is not +-0.  Eight lanes per (row, tile) slab: they fetch the
+// slab's first 32-byte sector (count word + 7 entries) in one round trip, which covers most
+// slabs at training densities, and only longer slabs loop on.
+// A CTA owns one 256-neuron tile over kActivityRows rows and counts into shared memory, so
+// a neuron that fires in many rows costs one global atomic per CTA instead of one per row
+// (with skewed firing rates the per-row form serialises on the hot neurons' addresses).
+constexpr int kActivityLanes = 8;
+constexpr int kActivityRows = 64;
+__global__ void __launch_bounds__(256)
+hyb_activity_count_kernel(const uint32_t* __restrict__ P, const uint32_t* __restrict__ vals,
+                          int M, int tiles, int W, int* __restrict__ active_rows) {
+  __shared__ int hist[kTileN];
+  const int t = blockIdx.x, r0 = blockIdx.y * kActivityRows;
+  const int r1 = min(r0 + kActivityRows, M);
+  const int g = threadIdx.x % kActivityLanes, lane = threadIdx.x & 31;
+  hist[threadIdx.x] = 0;
+  __syncthreads();
+  // every group runs the same number of iterations: the shuffle needs all lanes
+  for (int rb = r0; rb < r1; rb += 256 / kActivityLanes) {
+    const int r = rb + threadIdx.x / kActivityLanes;
+    const bool live = r < r1;
+    const size_t off = ((size_t)(live ? r : r0) * tiles + t) * W;
+    const uint32_t* s = P + off;
+    const uint32_t* v = vals != nullptr ? vals + off : s;
+    uint32_t pw = s[g];                          // W >= 32: the first 8 words always exist
+    uint32_t vw = vals != nullptr ? v[g] : pw;
+    int cnt = __shfl_sync(0xffffffffu, (int)pw, lane - g);
+    cnt = live ? min(max(cnt, 0), W - 1) : 0;
+    if (g >= 1 && g <= cnt && ((vw >> 16) & 0x7FFFu) != 0u) atomicAdd(&hist[pw & (kTileN - 1)], 1);
+    for (int i = kActivityLanes + g; i <= cnt; i += kActivityLanes) {
+      pw = s[i];
+      vw = vals != nullptr ? v[i] : pw;
+      if (((vw >> 16) & 0x7FFFu) != 0u) atomicAdd(&hist[pw & (kTileN - 1)], 1);
+    }
   }
+  __syncthreads();
+  const int n = hist[threadIdx.x];
+  if (n > 0) atomicAdd(&active_rows[t * kTileN + threadIdx.x], n);
 }
 
 // last_activated[j] = 0 for a neuron seen active, else + microbatch_tokens (:175-181).
@@ -504,8 +529,8 @@ int b200_hybrid_neuron_activity(const void* p_slab, const void* vals_slab, int64
   if (e != cudaSuccess) return fail(B200_ECUDA, "%s: memset: %s", fn, cudaGetErrorString(e));
   const int tiles = (int)(H / kTileN), W = kTileN / cf;
   if (M > 0) {
-    const int64_t slabs = M * tiles;
-    hyb_activity_count_kernel<<<(unsigned)((slabs + 7) / 8), 256, 0, st>>>(
+    const dim3 grid((unsigned)tiles, (unsigned)((M + kActivityRows - 1) / kActivityRows));
+    hyb_activity_count_kernel<<<grid, 256, 0, st>>>(
         static_cast<const uint32_t*>(p_slab), static_cast<const uint32_t*>(vals_slab), (int)M,
         tiles, W, active_rows);
   }
