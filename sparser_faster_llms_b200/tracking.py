@@ -124,23 +124,7 @@ class SparsityTracker:
         """Fused path with live dead-neuron counters: ``record_l0_l1`` plus the
         ``_last_activated`` update computed on the device from the forward's slabs ``P``
         (pattern) and ``T`` (``relu(gate)*up`` values)."""
-        from . import sparse_ops
-
-        if (not self.active) and torch.is_grad_enabled():
-            return
-        slab = P.slab if isinstance(P, sparse_ops.HybridSp) else P
-        if width is None:
-            width = (P.n if isinstance(P, sparse_ops.HybridSp)
-                     else slab.shape[1] // (sparse_ops.TILE // sparse_ops.compression_factor())
-                     * sparse_ops.TILE)
-        self.register_layer(layer_idx, width, slab.device)
-        self._l1_per_layer.append(l1)
-        if not self.active:
-            return
-        assert layer_idx == len(self._l0_per_layer)
-        self._l0_per_layer.append(l0)
-        sparse_ops.neuron_activity(P, T, last_activated=self._last_activated[layer_idx],
-                                   microbatch_tokens=self._microbatch_tokens, width=width)
+        record_pattern(self, layer_idx, l0, l1, P, T, width)
 
     def get_alive_neurons(self) -> List[torch.Tensor]:
         if self._number_of_layers is None:
@@ -163,6 +147,71 @@ class SparsityTracker:
         alive = [mask.mean() for mask in self.get_alive_neurons()]
         stats.update(get_tensor_stats_for_logging("activation_alive", alive))
         return l1_loss, stats
+
+
+def record_pattern(tracker, layer_idx: int, l0: torch.Tensor, l1: torch.Tensor, P, T=None,
+                   width: Optional[int] = None) -> None:
+    """``record_l0_l1`` with the dead-neuron counters kept live, for any tracker that has
+    the reference's fields (``active``, ``register_layer``, ``_l0_per_layer``,
+    ``_l1_per_layer``, ``_last_activated``, ``_microbatch_tokens``) - this module's
+    :class:`SparsityTracker` or the reference's own.  Trackers without those fields
+    (``NullTracker``) get the plain ``record_l0_l1`` call."""
+    from . import sparse_ops
+
+    if not hasattr(tracker, "_last_activated"):
+        tracker.record_l0_l1(layer_idx=layer_idx, l0=l0, l1=l1, width=width)
+        return
+    if (not tracker.active) and torch.is_grad_enabled():
+        return
+    slab = P.slab if isinstance(P, sparse_ops.HybridSp) else P
+    if width is None:
+        width = (P.n if isinstance(P, sparse_ops.HybridSp)
+                 else slab.shape[1] // (sparse_ops.TILE // sparse_ops.compression_factor())
+                 * sparse_ops.TILE)
+    tracker.register_layer(layer_idx, width, slab.device)
+    tracker._l1_per_layer.append(l1)
+    if not tracker.active:
+        return
+    assert layer_idx == len(tracker._l0_per_layer)
+    tracker._l0_per_layer.append(l0)
+    sparse_ops.neuron_activity(P, T, last_activated=tracker._last_activated[layer_idx],
+                               microbatch_tokens=tracker._microbatch_tokens, width=width)
+
+
+def fused_training_forward(mlp, hidden_states: torch.Tensor) -> torch.Tensor:
+    """The fused branch of ``SparseMLP.forward`` (sparse_models.py:378-395) with
+    ``record_pattern`` in place of ``record_l0_l1``.  ``mlp`` is a reference ``SparseMLP``
+    (or anything with ``gate_proj`` / ``up_proj`` / ``down_proj`` weights in the kernel
+    layout, ``tracker``, ``layer_idx``, ``intermediate_size``)."""
+    outs, l0, l1, P, _, T = torch.ops.sparse_ops.ff_forward_gated(
+        hidden_states, mlp.gate_proj.weight, mlp.up_proj.weight, mlp.down_proj.weight)
+    record_pattern(mlp.tracker, mlp.layer_idx, l0, l1, P, T, width=mlp.intermediate_size)
+    return outs
+
+
+def enable_live_dead_neuron_tracking(mlp) -> None:
+    """Patch one ``SparseMLP`` instance so that its fused training branch keeps the
+    dead-neuron counters current; every other branch (einsum training path, inference
+    logic) runs the module's own ``forward`` unchanged.  Idempotent; undo with
+    :func:`disable_live_dead_neuron_tracking`."""
+    if "_forward_without_live_tracking" in mlp.__dict__:
+        return
+    original = mlp.forward
+
+    def forward(hidden_states):
+        if (getattr(mlp, "_training_mode", False) and getattr(mlp, "_use_fast", False)
+                and getattr(mlp, "gated", False)):
+            return fused_training_forward(mlp, hidden_states)
+        return original(hidden_states)
+
+    mlp.__dict__["_forward_without_live_tracking"] = original
+    mlp.forward = forward
+
+
+def disable_live_dead_neuron_tracking(mlp) -> None:
+    original = mlp.__dict__.pop("_forward_without_live_tracking", None)
+    if original is not None:
+        del mlp.forward
 
 
 def select_fast_layers(l0_per_layer: Sequence, l0_cutoff: float) -> List[bool]:

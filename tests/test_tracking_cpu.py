@@ -75,6 +75,53 @@ def test_record_l0_l1_leaves_counters_stale_like_the_reference():
     assert float(stats["activation_l0/mean"]) == 3.0
 
 
+class _FakeSparseMLP(torch.nn.Module):
+    """The attributes of the reference's SparseMLP that the patch reads
+    (custom_models/sparse_models.py:262-395)."""
+
+    def __init__(self):
+        super().__init__()
+        self._training_mode, self._use_fast, self.gated = True, True, True
+        self.calls = []
+
+    def forward(self, hidden_states):
+        self.calls.append("own")
+        return hidden_states + 1
+
+
+def test_live_tracking_patch_routes_only_the_fused_training_branch(monkeypatch):
+    seen = []
+    monkeypatch.setattr(tracking, "fused_training_forward",
+                        lambda mlp, x: (seen.append(mlp), x * 2)[1])
+    mlp = _FakeSparseMLP()
+    x = torch.ones(2)
+    tracking.enable_live_dead_neuron_tracking(mlp)
+    tracking.enable_live_dead_neuron_tracking(mlp)          # idempotent
+    assert torch.equal(mlp(x), x * 2) and seen == [mlp] and mlp.calls == []
+    for attr in ("_use_fast", "_training_mode", "gated"):
+        setattr(mlp, attr, False)
+        assert torch.equal(mlp(x), x + 1)                   # the module's own forward
+        setattr(mlp, attr, True)
+    assert mlp.calls == ["own"] * 3 and len(seen) == 1
+    tracking.disable_live_dead_neuron_tracking(mlp)
+    tracking.disable_live_dead_neuron_tracking(mlp)
+    assert torch.equal(mlp(x), x + 1) and "forward" not in mlp.__dict__
+
+
+def test_record_pattern_function_falls_back_for_trackers_without_counters():
+    calls = []
+
+    class Plain:
+        def record_l0_l1(self, **kw):
+            calls.append(kw)
+
+    tracking.record_pattern(Plain(), 3, 1.0, 2.0, P=None, T=None, width=256)
+    assert calls == [{"layer_idx": 3, "l0": 1.0, "l1": 2.0, "width": 256}]
+    tr = tracking.SparsityTracker(4, 8, 1)                   # inactive + grad enabled: ignored
+    tracking.record_pattern(tr, 0, None, None, P=torch.zeros(2, 64, dtype=torch.int32))
+    assert tr._l1_per_layer == [] and tr._last_activated == {}
+
+
 def test_select_fast_layers():
     l0 = [torch.tensor(10.0), torch.tensor(200.0), 99.9]
     assert tracking.select_fast_layers(l0, 100) == [True, False, True]

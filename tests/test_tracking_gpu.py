@@ -86,6 +86,45 @@ def test_record_pattern_equals_record_activations_on_the_dense_activation():
     assert int(fused.get_alive_neurons()[0].sum()) > 0
 
 
+def test_patched_module_keeps_counters_live_through_forward_and_backward():
+    """A module with the reference SparseMLP's attributes (kernel-layout weights, tracker,
+    layer_idx; custom_models/sparse_models.py:262-395), patched: the fused training branch
+    runs under autograd and ages / revives the counters."""
+    torch.ops.sparse_ops_config.set_ell_width_regular(128)
+    d, h, b, s = 256, 512, 2, 32
+    ffn = synthetic.make_ffn(d, h, seed=9, density=0.05)
+
+    class Mlp(torch.nn.Module):
+        def __init__(self, tracker):
+            super().__init__()
+            lin = lambda w: torch.nn.Linear(w.shape[1], w.shape[0], bias=False)  # noqa: E731
+            self.gate_proj, self.up_proj, self.down_proj = lin(ffn.gate), lin(ffn.up), lin(ffn.down)
+            for m, w in ((self.gate_proj, ffn.gate), (self.up_proj, ffn.up), (self.down_proj, ffn.down)):
+                m.weight.data = w.clone()
+            with torch.no_grad():
+                self.gate_proj.weight[:50] = 0                  # neurons 0..49 never fire
+            self.tracker, self.layer_idx, self.intermediate_size = tracker, 0, h
+            self._training_mode, self._use_fast, self.gated = True, True, True
+
+        def forward(self, x):
+            raise AssertionError("the fused branch must not reach the module's own forward")
+
+    tr = tracking.SparsityTracker(b, s, b, tokens_until_dead=b * s)
+    mlp = Mlp(tr).to(DEV).to(torch.bfloat16)
+    tracking.enable_live_dead_neuron_tracking(mlp)
+    for step in range(2):
+        x = synthetic.make_tokens(b * s, d, seed=60 + step).reshape(b, s, d).to(DEV).requires_grad_(True)
+        tr.start_forward_pass()
+        out = mlp(x)
+        l1, stats = tr.finalize_forward_pass()
+        (out.float().sum() + 0.01 * l1).backward()
+        assert x.grad is not None and mlp.gate_proj.weight.grad is not None
+        assert int(tr._last_activated[0][:50].min()) == (step + 1) * b * s
+    alive = tr.get_alive_neurons()[0]
+    assert int(alive[:50].sum()) == 0 and int(alive.sum()) > 0
+    assert float(stats["activation_l0/mean"]) > 0
+
+
 def test_hybridsp_wrappers_empty_input_and_argument_errors():
     torch.ops.sparse_ops_config.set_ell_width_regular(128)
     ffn = synthetic.make_ffn(256, 512, seed=3, density=0.05)
