@@ -2,8 +2,12 @@
 reference's SparsityTracker (custom_models/sparse_models.py:95-256; generator:
 tests/golden/make_golden.py --only-tracker), and the oracle's slab-level activity count
 against the dense definition."""
+import contextlib
 import importlib.util
+import io
 import json
+import os
+import sys
 from pathlib import Path
 
 import numpy as np
@@ -106,6 +110,57 @@ def test_live_tracking_patch_routes_only_the_fused_training_branch(monkeypatch):
     tracking.disable_live_dead_neuron_tracking(mlp)
     tracking.disable_live_dead_neuron_tracking(mlp)
     assert torch.equal(mlp(x), x + 1) and "forward" not in mlp.__dict__
+
+
+REFERENCE = Path(os.environ.get("SPARSER_REFERENCE_ROOT",
+                                Path(__file__).resolve().parents[2] / "reference"))
+
+
+@pytest.mark.skipif(not (REFERENCE / "custom_models").exists(),
+                    reason="reference checkout not present on this machine")
+def test_patch_fits_the_reference_sparse_mlp(monkeypatch):
+    """The reference's own SparseMLP (custom_models/sparse_models.py:259-410), built with
+    use_hybrid_kernel=True over this package's operator loader: the patch takes over the
+    fused training branch and leaves the einsum branch to the module."""
+    from sparser_faster_llms_b200 import dropin
+    saved = {k: v for k, v in sys.modules.items() if k.startswith("custom_models")}
+    for k in saved:
+        del sys.modules[k]
+    sys.path.insert(0, str(REFERENCE))
+    try:
+        dropin.install()
+        from transformers import LlamaConfig
+        from custom_models import sparse_models as ref
+        with contextlib.redirect_stdout(io.StringIO()):
+            tr = ref.SparsityTracker(train_batch_size=2, max_seq_len=8,
+                                     per_device_train_batch_size=2, gated=True)
+        cfg = LlamaConfig(hidden_size=256, intermediate_size=512, mlp_bias=False)
+        mlp = ref.SparseMLP(layer_idx=0, config=cfg, gated=True, tracker=tr,
+                            execution_logic="training", use_hybrid_kernel=True)
+        assert mlp.down_proj.weight.shape == (512, 256)       # kernel layout [H, D]
+        seen = []
+        monkeypatch.setattr(tracking, "fused_training_forward",
+                            lambda m, x: (seen.append(m), x)[1])
+        tracking.enable_live_dead_neuron_tracking(mlp)
+        x = torch.randn(2, 8, 256)
+        mlp.enable_fast(True)
+        assert mlp(x) is x and seen == [mlp]
+        mlp.enable_fast(False)                                # einsum branch, reference code
+        tr.start_forward_pass()
+        y = mlp(x)
+        assert y.shape == x.shape and len(seen) == 1 and len(tr._l0_per_layer) == 1
+        # the module-level record_pattern accepts the reference's tracker object as it is
+        for field in ("active", "register_layer", "_l0_per_layer", "_l1_per_layer",
+                      "_last_activated", "_microbatch_tokens"):
+            assert hasattr(tr, field), field
+        tracking.disable_live_dead_neuron_tracking(mlp)
+        assert "forward" not in mlp.__dict__
+    finally:
+        sys.path.remove(str(REFERENCE))
+        dropin.uninstall()
+        for k in [k for k in sys.modules if k.startswith("custom_models")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
 
 
 def test_record_pattern_function_falls_back_for_trackers_without_counters():
