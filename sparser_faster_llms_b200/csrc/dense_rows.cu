@@ -591,11 +591,30 @@ int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void
     if (int rc = make_map(&map_a1, a1, a_rows, K, 128, KS)) return rc;
     if (int rc = make_map(&map_b, b, b_rows, K, kDenseTok, KS)) return rc;
   }
+  dim3 grid((unsigned)(a_rows / (DUAL ? 128 : 256)), (unsigned)((cap + kDenseTok - 1) / kDenseTok), 1);
+  // A grid of at most one CTA per SM (the weight-gradient products at d_model 1024: 128
+  // tiles with K = all tokens) gets a ring twice as deep: the second co-resident CTA that
+  // would otherwise double the bytes in flight does not exist there.
+  static const bool deep_ring = [] {
+    const char* e = getenv("B200_DENSE_DEEP_RING");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  if (KS == 64 && deep_ring && (int64_t)grid.x * grid.y <= (int64_t)sm_count()) {
+    constexpr int DEEP = 2 * kDenseStages;
+    const size_t smem_deep = (size_t)DEEP * (2 * 128 * 64 * 2 + kDenseTok * 64 * 2) + 1024;
+    auto deep = dense_rows_gemm_kernel<kDenseTok, DEEP, DUAL, 64>;
+    static size_t granted_deep[64] = {0};
+    if (int rc = ensure_dynamic_smem(deep, smem_deep, granted_deep, "b200_twell_gated_t2d_hybrid"))
+      return rc;
+    deep<<<grid, kThreadsTc, smem_deep, stream>>>(map_a0, map_a1, map_b, bias,
+                                                  static_cast<__nv_bfloat16*>(out), row_ids,
+                                                  n_rows_ptr, (int)cap, (int)K, (int)ld_out);
+    return check_launch("b200_twell_gated_t2d_hybrid (dense rows, deep ring)");
+  }
   const size_t smem = (size_t)STAGES * (2 * 128 * KS * 2 + kDenseTok * KS * 2) + 1024;
   auto kern = dense_rows_gemm_kernel<kDenseTok, STAGES, DUAL, KS>;
   static size_t granted[64] = {0};
   if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_gated_t2d_hybrid")) return rc;
-  dim3 grid((unsigned)(a_rows / (DUAL ? 128 : 256)), (unsigned)((cap + kDenseTok - 1) / kDenseTok), 1);
   kern<<<grid, kThreadsTc, smem, stream>>>(map_a0, map_a1, map_b, bias,
                                            static_cast<__nv_bfloat16*>(out), row_ids, n_rows_ptr,
                                            (int)cap, (int)K, (int)ld_out);
