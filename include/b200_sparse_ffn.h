@@ -126,6 +126,45 @@ int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias
                          void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The fused gated MLP as ONE kernel for decode-sized calls (1 <= M <= 32): a thread-block
+ * cluster per 256-neuron tile computes its slice of the gate, writes the slab words (same
+ * bytes as b200_twell_pack) and at once contracts its own active neurons - every active up /
+ * down row is fetched once per call, staged in shared memory by cp.async.bulk, however many
+ * tokens fire it - and the tiles' partial sums meet in the workspace.  Replaces the
+ * reference's two launches per layer (custom_models/twell_modules/mlp_twell.cu:126-152:
+ * matmul_d2t.cu:287-709 followed by matmul_gated_t2d.cu:17-169).
+ *   workspace: at least b200_twell_decode_workspace_bytes(M, D, H) bytes (0 = this shape is
+ *     not served), 16-byte aligned, zero-filled once before its first use; it may be the
+ *     same buffer that the other contraction entry points use.  Calls that can overlap on
+ *     the GPU need different workspaces.
+ *   prefetch / prefetch_bytes: optional range of this GPU's memory (16-byte aligned) that the
+ *     kernel asks L2 to prefetch while it runs, e.g. the next layer's gate matrix, which does
+ *     not depend on this layer's result; NULL / 0 = none.
+ * The CTAs of the grid wait for one another (bounded): the call needs the GPU to itself while
+ * it runs; the host checks with cudaOccupancyMaxActiveClusters that the grid is resident at
+ * once.  Returns B200_EUNSUPPORTED when the shape, the workspace or the residency check rules
+ * the kernel out: use b200_twell_gated_mlp, which makes this choice itself (it takes this
+ * path whenever its workspace argument is large enough; the environment variable
+ * B200_DECODE_FUSED=0 keeps the two-kernel form).
+ */
+size_t b200_twell_decode_workspace_bytes(int64_t M, int64_t D, int64_t H);
+
+int b200_twell_gated_mlp_decode(const void* x, const void* gate, const float* gate_bias,
+                                const void* up, const void* down, void* packed, void* out,
+                                int64_t M, int64_t D, int64_t H, int cf, uint32_t flags,
+                                void* workspace, size_t workspace_bytes, const void* prefetch,
+                                int64_t prefetch_bytes, void* stream);
+
+/* Error word of the fused decode kernel: 0, or the wait that gave up (1 producer, 2 mma,
+ * 3 accumulator, 4 up rows, 5 down rows, 6 cross-tile barrier); -1 if it cannot be read.
+ * Reads and clears the word; synchronises the device. */
+int b200_twell_decode_status(void);
+
+/* Asks L2 to prefetch [ptr, ptr + bytes) of this GPU's memory (cp.async.bulk.prefetch.L2,
+ * one small kernel on `stream`).  A hint: no result depends on it.  No reference counterpart. */
+int b200_l2_prefetch(const void* ptr, int64_t bytes, void* stream);
+
+/*
  * Fused non-gated MLP: pack(relu(x @ up^T)) then the down projection.
  * Replaces TWELL_MLP::run_mlp_layer* (custom_models/twell_modules/mlp_twell.cu:73-98).
  */

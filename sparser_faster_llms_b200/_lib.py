@@ -95,6 +95,14 @@ _PROTOTYPES = {
     "b200_twell_gated_mlp": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_int64, c_int64, c_int64, c_int, c_uint32,
                                      c_void_p, c_size_t, c_void_p]),
+    "b200_twell_decode_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    # x, gate, gate_bias, up, down, packed, out, M, D, H, cf, flags, ws, ws_bytes, prefetch,
+    # prefetch_bytes, stream
+    "b200_twell_gated_mlp_decode": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int64, c_int,
+                                            c_uint32, c_void_p, c_size_t, c_void_p, c_int64,
+                                            c_void_p]),
+    "b200_twell_decode_status": (c_int, []),
+    "b200_l2_prefetch": (c_int, [c_void_p, c_int64, c_void_p]),
     "b200_twell_mlp": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
 }

@@ -40,6 +40,29 @@ int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, con
                      void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream,
                      const unsigned char* skip_rows = nullptr, const FusedAr* fused_ar = nullptr);
 
+size_t twell_decode_workspace_bytes(int64_t M, int64_t D, int64_t H);
+int twell_decode_launch(bool gated, bool hp, const void* x, const void* gate, const float* bias,
+                        const void* up, const void* down, void* packed, void* out, int64_t M,
+                        int64_t D, int64_t H, int cf, void* workspace, size_t workspace_bytes,
+                        const void* pf_ptr, int64_t pf_bytes, cudaStream_t stream,
+                        bool probe_only);
+int l2_prefetch_launch(const void* p, int64_t bytes, cudaStream_t stream);
+int twell_decode_status();
+#ifdef B200_TRACE
+void twell_decode_trace(unsigned long long* out16);
+#endif
+
+// Whether b200_twell_gated_mlp / b200_twell_mlp hand decode-sized calls to the fused one-kernel
+// form when the caller's workspace is large enough (B200_DECODE_FUSED=0 keeps two kernels).
+bool decode_fused_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("B200_DECODE_FUSED");
+    on = (e != nullptr && atoi(e) == 0) ? 0 : 1;
+  }
+  return on != 0;
+}
+
 int pdl_mask() {
   static int mask = -1;
   if (mask < 0) {
@@ -188,10 +211,79 @@ int b200_hybrid_spmm(const void* vals_slab, const void* b_rows, void* out, int64
                           static_cast<cudaStream_t>(stream));
 }
 
+size_t b200_twell_decode_workspace_bytes(int64_t M, int64_t D, int64_t H) {
+  if (M < 0 || D <= 0 || H <= 0 || D % 256 || H % 256) return 0;
+  return twell_decode_workspace_bytes(M, D, H);
+}
+
+int b200_twell_decode_status(void) { return twell_decode_status(); }
+
+#ifdef B200_TRACE
+void b200_debug_trace_decode(unsigned long long* out16) { twell_decode_trace(out16); }
+#endif
+
+int b200_l2_prefetch(const void* ptr, int64_t bytes, void* stream) {
+  const char* fn = "b200_l2_prefetch";
+  if (bytes < 0) return fail(B200_EINVAL, "%s: bytes must be >= 0", fn);
+  if (bytes == 0) return B200_OK;
+  B200_TRY(check_ptr(fn, "ptr", ptr));
+  return l2_prefetch_launch(ptr, bytes, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+// Argument checks shared by the fused decode entry points.
+int check_decode_args(const char* fn, const void* x, const void* gate, const float* gate_bias,
+                      const void* up, const void* down, const void* packed, const void* out,
+                      int64_t M, int64_t D, int64_t H, int cf, uint32_t flags, const void* ws,
+                      bool gated) {
+  B200_TRY(check_dims(fn, M, D, H, cf));
+  if (flags & ~B200_FLAG_HIGH_PRECISION) return fail(B200_EINVAL, "%s: unknown flags 0x%x", fn, flags);
+  if (M == 0) return B200_OK;
+  B200_TRY(check_ptr(fn, "x", x));
+  B200_TRY(check_ptr(fn, gated ? "gate" : "up", gate));
+  if (gated) B200_TRY(check_ptr(fn, "up", up));
+  B200_TRY(check_ptr(fn, "down", down));
+  B200_TRY(check_ptr(fn, "packed", packed));
+  B200_TRY(check_ptr(fn, "out", out));
+  B200_TRY(check_workspace(fn, ws));
+  if (gate_bias != nullptr && (reinterpret_cast<uintptr_t>(gate_bias) & 3u))
+    return fail(B200_EALIGN, "%s: bias is not 4-byte aligned", fn);
+  return B200_OK;
+}
+}  // namespace
+
+int b200_twell_gated_mlp_decode(const void* x, const void* gate, const float* gate_bias,
+                                const void* up, const void* down, void* packed, void* out,
+                                int64_t M, int64_t D, int64_t H, int cf, uint32_t flags,
+                                void* workspace, size_t workspace_bytes, const void* prefetch,
+                                int64_t prefetch_bytes, void* stream) {
+  const char* fn = "b200_twell_gated_mlp_decode";
+  B200_TRY(check_decode_args(fn, x, gate, gate_bias, up, down, packed, out, M, D, H, cf, flags,
+                             workspace, true));
+  if (M == 0) return B200_OK;
+  if (prefetch != nullptr && (!aligned16(prefetch) || prefetch_bytes < 0))
+    return fail(B200_EALIGN, "%s: prefetch range must be 16-byte aligned and non-negative", fn);
+  return twell_decode_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, gate, gate_bias, up,
+                             down, packed, out, M, D, H, cf, workspace, workspace_bytes, prefetch,
+                             prefetch != nullptr ? prefetch_bytes : 0,
+                             static_cast<cudaStream_t>(stream), false);
+}
+
 int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias, const void* up,
                          const void* down, void* packed, void* out, int64_t M, int64_t D,
                          int64_t H, int cf, uint32_t flags, void* workspace,
                          size_t workspace_bytes, void* stream) {
+  if (M >= 1 && M <= 32 && workspace != nullptr && decode_fused_enabled() &&
+      workspace_bytes >= twell_decode_workspace_bytes(M, D, H) &&
+      twell_decode_workspace_bytes(M, D, H) > 0) {
+    B200_TRY(check_decode_args("b200_twell_gated_mlp", x, gate, gate_bias, up, down, packed, out,
+                               M, D, H, cf, flags, workspace, true));
+    const int rc = twell_decode_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, gate,
+                                       gate_bias, up, down, packed, out, M, D, H, cf, workspace,
+                                       workspace_bytes, nullptr, 0,
+                                       static_cast<cudaStream_t>(stream), false);
+    if (rc != B200_EUNSUPPORTED) return rc;  // served (or failed for good)
+  }
   B200_TRY(b200_twell_pack(x, gate, gate_bias, packed, M, D, H, cf, stream));
   return b200_twell_gated_t2d(x, packed, up, down, out, M, D, H, cf, flags, workspace,
                               workspace_bytes, stream);
@@ -264,6 +356,17 @@ int b200_fused_allreduce_status(void* my_block) {
 int b200_twell_mlp(const void* x, const void* up, const void* down, void* packed, void* out,
                    int64_t M, int64_t D, int64_t H, int cf, int num_splits, void* workspace,
                    size_t workspace_bytes, void* stream) {
+  if (M >= 1 && M <= 32 && workspace != nullptr && decode_fused_enabled() &&
+      (num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8) &&
+      workspace_bytes >= twell_decode_workspace_bytes(M, D, H) &&
+      twell_decode_workspace_bytes(M, D, H) > 0) {
+    B200_TRY(check_decode_args("b200_twell_mlp", x, up, nullptr, nullptr, down, packed, out, M, D,
+                               H, cf, 0, workspace, false));
+    const int rc = twell_decode_launch(false, false, x, up, nullptr, nullptr, down, packed, out, M,
+                                       D, H, cf, workspace, workspace_bytes, nullptr, 0,
+                                       static_cast<cudaStream_t>(stream), false);
+    if (rc != B200_EUNSUPPORTED) return rc;
+  }
   B200_TRY(b200_twell_pack(x, up, nullptr, packed, M, D, H, cf, stream));
   return b200_twell_t2d(packed, down, out, M, D, H, cf, num_splits, workspace, workspace_bytes,
                         stream);

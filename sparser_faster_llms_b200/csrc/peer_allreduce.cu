@@ -36,6 +36,7 @@ constexpr int kMaxWorld = 8;
 constexpr int kArCtas = 32;
 constexpr int kArThreads = 256;
 constexpr uint32_t kArSpinLimit = 1u << 22;
+constexpr uint32_t kArShortSpinLimit = 1u << 10;  // once the error word is set
 // control block (uint32 words): epoch of the last finished call per CTA, then the error word
 constexpr int kEpochOff = 0;
 constexpr int kErrorOff = kArCtas;
@@ -75,7 +76,7 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
 __global__ void __launch_bounds__(kArThreads)
 peer_allreduce_kernel(const __grid_constant__ PeerBlocks peers, const uint4* __restrict__ local_in, uint4* __restrict__ out,
                       int rank, int world, int64_t n_vec, int64_t slot_bytes) {
-  __shared__ uint32_t epoch_s;
+  __shared__ uint32_t epoch_s, limit_s;
   const int tid = threadIdx.x;
   unsigned char* my_block = nullptr;  // unrolled select: no runtime index into the parameter
 #pragma unroll
@@ -86,9 +87,17 @@ peer_allreduce_kernel(const __grid_constant__ PeerBlocks peers, const uint4* __r
   const int64_t first = (int64_t)blockIdx.x * kArThreads + tid;
   uint4 mine = make_uint4(0u, 0u, 0u, 0u);
   if (first < n_vec) mine = local_in[first];  // in flight while the epoch is read
-  if (tid == 0) epoch_s = *reinterpret_cast<volatile uint32_t*>(ctl + kEpochOff + blockIdx.x) + 1u;
+  if (tid == 0) {
+    epoch_s = *reinterpret_cast<volatile uint32_t*>(ctl + kEpochOff + blockIdx.x) + 1u;
+    // The error word is sticky until the host reads it: once a peer has failed to arrive,
+    // every later wait (of this call and of the following calls) gives up after a short
+    // spin, so a dead or late rank costs microseconds per call instead of seconds.
+    limit_s = *reinterpret_cast<volatile uint32_t*>(ctl + kErrorOff) != 0u ? kArShortSpinLimit
+                                                                             : kArSpinLimit;
+  }
   __syncthreads();
   const uint32_t e = epoch_s;
+  uint32_t limit = limit_s;
   // flagged slots are twice the payload: 2 * slot_bytes per (parity, source rank)
   const size_t inbox_off = kControlBytes + (size_t)(e & 1u) * kMaxWorld * 2 * (size_t)slot_bytes;
 
@@ -127,8 +136,9 @@ peer_allreduce_kernel(const __grid_constant__ PeerBlocks peers, const uint4* __r
         if (!((pending >> p) & 1u)) continue;
         if (lo[p].y == e && lo[p].w == e && hi[p].y == e && hi[p].w == e) pending &= ~(1u << p);
       }
-      if (pending && ++spins >= kArSpinLimit) {
+      if (pending && ++spins >= limit) {
         atomicExch(ctl + kErrorOff, 0x100u + (uint32_t)(__ffs(pending) - 1));  // who is missing
+        limit = kArShortSpinLimit;
         break;
       }
     }

@@ -29,6 +29,7 @@
 // barrier / counter that precedes the first store.
 #include <cooperative_groups.h>
 
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -64,6 +65,7 @@ __device__ __forceinline__ uint4 ldg_nc(const void* p) {
 // The inbox is double-buffered by the epoch's parity (a pair is rewritten two calls later,
 // which a peer can reach only after this rank has finished the call in between).
 constexpr uint32_t kFarSpinLimit = 1u << 22;
+constexpr uint32_t kFarShortSpinLimit = 1u << 10;  // once the error word is set (sticky)
 
 __device__ __forceinline__ uint32_t bf162_bits(__nv_bfloat162 v) {
   return *reinterpret_cast<uint32_t*>(&v);
@@ -84,7 +86,7 @@ __device__ __forceinline__ void far_push(const FusedAr& ar, size_t inbox_off, si
 // Sum over ranks, in rank order, of the bf16 pairs of one position; `mine` is this rank's.
 __device__ __forceinline__ float2 far_gather(const FusedAr& ar, const unsigned char* my_inbox,
                                              size_t pair, uint32_t mine, uint32_t e,
-                                             uint32_t* err) {
+                                             uint32_t* err, uint32_t& limit) {
   float s0 = 0.f, s1 = 0.f;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
@@ -98,8 +100,11 @@ __device__ __forceinline__ float2 far_gather(const FusedAr& ar, const unsigned c
                      : "=r"(payload), "=r"(flag)
                      : "l"(src)
                      : "memory");
-      } while (flag != e && ++spins < kFarSpinLimit);
-      if (flag != e) atomicExch(err, 0x100u + (uint32_t)p);  // this peer never arrived
+      } while (flag != e && ++spins < limit);
+      if (flag != e) {
+        atomicExch(err, 0x100u + (uint32_t)p);  // this peer never arrived
+        limit = kFarShortSpinLimit;             // the remaining waits of this thread drain fast
+      }
     }
     const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&payload));
     s0 += f.x;
@@ -125,7 +130,7 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
   __shared__ float usum[2][GATED ? kDepth : 1][GATED ? NI : 1];  // double-buffered per batch
   __shared__ __align__(16) float inbox[D];  // [cs][D / cs]: column sums pushed by the cluster
   __shared__ int is_last;
-  __shared__ uint32_t epoch_s;
+  __shared__ uint32_t epoch_s, far_limit_s;
   __shared__ __align__(16) uint32_t slab_s[kStageWords];
 
   cg::cluster_group cluster = cg::this_cluster();
@@ -146,8 +151,14 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
 #pragma unroll
   for (int p = 0; p < 8; ++p)
     if (p == ar.rank) my_block = ar.block[p];
-  if (fused && tid == 0)
+  if (fused && tid == 0) {
     epoch_s = reinterpret_cast<volatile uint32_t*>(my_block)[kFarEpochWord] + 1u;
+    // The error word stays set until the host reads it: after one peer failed to arrive,
+    // later waits (this call and the following ones) give up after a short spin.
+    far_limit_s = reinterpret_cast<volatile uint32_t*>(my_block)[kFarErrorWord] != 0u
+                      ? kFarShortSpinLimit
+                      : kFarSpinLimit;
+  }
   const uint32_t* prow = packed + (size_t)row * tiles * slab_w;
   // Remote shared memory may only be touched once every CTA of the cluster runs:
   // arrive now, wait right before the first remote store.
@@ -357,12 +368,13 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
   auto collect = [&]() {
     if (!fused) return;
     uint32_t* ctl = reinterpret_cast<uint32_t*>(my_block);
+    uint32_t limit = far_limit_s;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int c = 2 * (tid + k * NTHREADS);
       if (c >= cols) break;
       const float2 s = far_gather(ar, my_block + inbox_off, pair0 + (c >> 1), bf162_bits(mine[k]),
-                                  e, ctl + kFarErrorWord);
+                                  e, ctl + kFarErrorWord, limit);
       *reinterpret_cast<__nv_bfloat162*>(orow + c) = __floats2bfloat162_rn(s.x, s.y);
     }
     __syncthreads();
@@ -448,6 +460,28 @@ int launch_t2d(const void* x, const void* packed, const void* up, const void* do
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (ar.world > 1) {
+    // A CTA of the fused form waits for remote data, and its peers wait for the data of every
+    // CTA of this grid: all clusters must be resident at once.  Ask the occupancy calculator
+    // for this kernel, block size and cluster size (cached per device and cluster size).
+    static int max_clusters[64][4] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    const int slot = cs == 1 ? 0 : cs == 2 ? 1 : cs == 4 ? 2 : 3;
+    if (max_clusters[dev][slot] == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = -1;
+      }
+      max_clusters[dev][slot] = n;
+    }
+    if (M * nc > (int64_t)max_clusters[dev][slot])
+      return fail(B200_EUNSUPPORTED,
+                  "twell_t2d: the fused all-reduce needs all %lld clusters of %d CTAs resident at "
+                  "once (limit %d)", (long long)(M * nc), cs, max_clusters[dev][slot]);
+  }
   cfg.numAttrs = add_pdl_attribute(attr, 1, 2);
   cudaError_t e = cudaLaunchKernelEx(
       &cfg, kern, reinterpret_cast<const __nv_bfloat16*>(x),
@@ -480,8 +514,11 @@ int dispatch_ni(int ni, const void* x, const void* packed, const void* up, const
 
 }  // namespace
 
-// Workspace layout: [kCounterWords counters][fp32 partial sums].
+// Workspace layout: [kCounterWords words][fp32 partial sums].  The first kT2dCounterWords
+// words are this kernel's arrival counters; the last 64 words of the block belong to the
+// cross-tile barrier of the fused decode kernel (twell_decode.cu).
 constexpr size_t kCounterWords = 4096;
+constexpr size_t kT2dCounterWords = kCounterWords - 64;
 
 // Launch shape.  cs: CTAs per cluster (D / cs must stay a multiple of 8 columns).
 // nc: clusters per token - more than one only when there are few tokens and the
@@ -491,7 +528,7 @@ void t2d_shape(int64_t M, int64_t D, int sm_count, size_t workspace_bytes, int* 
   int cs = 1;
   while (cs < 8 && M * cs * 2 <= (int64_t)sm_count * 2 && (D / (cs * 2)) % 8 == 0) cs *= 2;
   int nc = 1;
-  if (workspace_bytes > kCounterWords * 4 && M * 8 <= (int64_t)kCounterWords) {
+  if (workspace_bytes > kCounterWords * 4 && M * 8 <= (int64_t)kT2dCounterWords) {
     const int64_t cap_floats = (int64_t)((workspace_bytes - kCounterWords * 4) / 4);
     int64_t want = ((int64_t)sm_count * 2) / (M * cs);  // about two CTAs per SM in total
     // Clusters per token are capped: every extra cluster adds a partial sum to the final
@@ -519,7 +556,8 @@ int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, con
   t2d_shape(M, D, sm_count, workspace != nullptr ? workspace_bytes : 0, &cs, &nc);
   FusedAr far = {};
   if (fused_ar != nullptr && fused_ar->world > 1) {
-    // Every CTA must be resident while it waits for the peers.
+    // Every CTA must be resident while it waits for the peers (the exact residency check
+    // is made against the occupancy calculator at launch).
     if (M * nc * cs > 2 * (int64_t)sm_count || M > kFarMaxTokens)
       return fail(B200_EUNSUPPORTED,
                   "twell_t2d: the fused all-reduce serves at most %d tokens in one wave (M = %lld)",
@@ -568,8 +606,10 @@ constexpr size_t kStaticScratchBytes = (size_t)1 << 20;  // counters + fp32 part
 // cudaGetSymbolAddress; it is never passed to a kernel directly.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-// Device address of g_static_scratch per device ordinal, resolved on first use.
-void* g_static_scratch_ptr[64] = {nullptr};
+// Device address of g_static_scratch per device ordinal, resolved on first use.  Atomic:
+// two host threads may make their first call on a device at the same time (both store the
+// same address).
+std::atomic<void*> g_static_scratch_ptr[64];
 
 int static_scratch_address(void** out) {
   int dev = 0;
@@ -580,15 +620,15 @@ int static_scratch_address(void** out) {
   if (dev < 0 || dev >= 64)
     return b200::fail(B200_EUNSUPPORTED,
                       "b200_twell_gated_t2d_noalloc: device ordinal %d is outside 0..63", dev);
-  if (g_static_scratch_ptr[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     e = cudaGetSymbolAddress(&p, g_static_scratch);  // address on the CURRENT device
     if (e != cudaSuccess || p == nullptr)
       return b200::fail(B200_ECUDA, "b200_twell_gated_t2d_noalloc: cudaGetSymbolAddress: %s",
                         cudaGetErrorString(e));
-    g_static_scratch_ptr[dev] = p;
+    g_static_scratch_ptr[dev].store(p, std::memory_order_release);
   }
-  *out = g_static_scratch_ptr[dev];
+  *out = p;
   return B200_OK;
 }
 
@@ -597,7 +637,7 @@ int static_scratch_address(void** out) {
 int noalloc_max_tokens(int64_t D) {
   const int64_t cap_floats = (int64_t)((kStaticScratchBytes - b200::kCounterWords * 4) / 4);
   const int64_t by_partials = cap_floats / (2 * D);
-  const int64_t by_counters = (int64_t)b200::kCounterWords / 8;
+  const int64_t by_counters = (int64_t)b200::kT2dCounterWords / 8;
   return (int)(by_partials < by_counters ? by_partials : by_counters);
 }
 
@@ -629,9 +669,12 @@ extern "C" int b200_twell_gated_t2d_noalloc(const void* x, const void* packed, c
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The array keeps whatever the previous call left behind: the arrival counters
   // must start at zero (the partial sums are fully overwritten before they are read).
-  cudaError_t e = cudaMemsetAsync(scratch, 0, b200::kCounterWords * sizeof(unsigned int), st);
+  cudaError_t e = cudaMemsetAsync(scratch, 0, b200::kT2dCounterWords * sizeof(unsigned int), st);
   if (e != cudaSuccess)
-    return b200::fail(B200_ECUDA, "%s: cudaMemsetAsync: %s", fn, cudaGetErrorString(e));
+    return b200::fail(B200_ECUDA,
+                      "%s: cudaMemsetAsync: %s (the stream must belong to the current device, "
+                      "whose copy of the scratch array this call uses)", fn,
+                      cudaGetErrorString(e));
   b200::pdl_suppressed() = true;  // the predecessor of this launch is the memset above
   const int rc = b200::twell_t2d_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, packed,
                                         up, down, out, M, D, H, cf, scratch, kStaticScratchBytes,

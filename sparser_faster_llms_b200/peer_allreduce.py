@@ -7,17 +7,31 @@ At decode sizes (4..128 KB) this replaces an NCCL all-reduce whose latency is la
 the sharded FFN itself.  One object serves every layer of a model: its inbox is
 double-buffered by a device-side epoch, and the launch is safe to capture in a CUDA graph.
 
-No multicast / NVLS is used (plain peer stores and local loads), so a rank that dies
-cannot wedge the switch; a missing peer shows up as a non-zero ``status()``.
+The kernels use plain peer stores and local loads only.  torch's symmetric-memory
+rendezvous would by default also bind the block to an NVLink multicast object on NVSwitch
+machines; that binding buys these kernels nothing and a rank that exits while bound can
+raise NVLink faults on its peers, so ``_disable_symm_mem_multicast()`` switches it off
+(``TORCH_SYMM_MEM_DISABLE_MULTICAST=1``) before the first symmetric allocation of the
+process.  ``NCCL_NVLS_ENABLE`` only governs NCCL's own collectives.  Call ``close()`` on
+these objects (then synchronise) before the process leaves, so no mapping of a peer's
+memory is still held at exit.  A missing peer shows up as a non-zero ``status()``; the
+error word is sticky: after it is set, later waits give up after a short spin until
+``status()`` has read and cleared it.
 """
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
 
 from . import _lib
+
+
+def _disable_symm_mem_multicast() -> None:
+    """Keep torch symmetric memory from binding blocks to an NVLink multicast object."""
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 
 class FusedShardAllReduce:
@@ -32,6 +46,7 @@ class FusedShardAllReduce:
 
     def __init__(self, max_tokens: int, d_model: int, *, group=None,
                  device: torch.device | None = None):
+        _disable_symm_mem_multicast()
         import torch.distributed._symmetric_memory as symm_mem
         if not dist.is_initialized():
             raise RuntimeError("FusedShardAllReduce needs an initialised process group")
@@ -58,7 +73,17 @@ class FusedShardAllReduce:
         dist.barrier(self.group)  # every block is zeroed before anyone may push into it
 
     def serves(self, tokens: int, d_model: int) -> bool:
-        return tokens <= self.max_tokens and d_model == self.d_model
+        return (self.block is not None and tokens <= self.max_tokens
+                and d_model == self.d_model)
+
+    def close(self) -> None:
+        """Release the symmetric block and the peer mappings (idempotent).  Call on every
+        rank between steps, with no kernel of this object in flight."""
+        if self.block is not None:
+            torch.cuda.synchronize(self.device)
+        self.handle = None
+        self.block = None
+        self.ptr_array = None
 
     def status(self) -> int:
         """0, or ``0x100 + peer`` if a wait for that peer gave up.  Synchronises the device."""
@@ -68,6 +93,7 @@ class FusedShardAllReduce:
 
 class PeerAllReduce:
     def __init__(self, max_bytes: int, *, group=None, device: torch.device | None = None):
+        _disable_symm_mem_multicast()
         import torch.distributed._symmetric_memory as symm_mem
         if not dist.is_initialized():
             raise RuntimeError("PeerAllReduce needs an initialised process group")
@@ -111,3 +137,15 @@ class PeerAllReduce:
         """0, or ``0x100 + peer`` if a wait for that peer gave up.  Synchronises the device."""
         with torch.cuda.device(self.device):
             return int(_lib.load_library().b200_peer_allreduce_status(self.block.data_ptr()))
+
+    def close(self) -> None:
+        """Release the symmetric block and the peer mappings (idempotent).  Call on every
+        rank between steps, with no kernel of this object in flight."""
+        if self.block is not None:
+            torch.cuda.synchronize(self.device)
+        fused = getattr(self, "fused", None)
+        if fused is not None:
+            fused.close()
+        self.handle = None
+        self.block = None
+        self._ptr_array = None

@@ -185,6 +185,25 @@ class ShardedTwELLGatedMLP(nn.Module):
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.process_group)
         return y
 
+    def check_status(self) -> int:
+        """Error words of the peer-memory all-reduces this module uses: 0, or ``0x100 + peer``
+        if a bounded wait for that peer gave up since the last check (the sums of such a call
+        are invalid).  Reads and clears the words and synchronises the device, so call it once
+        per step, not per layer.  After a non-zero status the module stops using the peer
+        kernels and sums through the process group (NCCL) from the next call on."""
+        status = 0
+        for obj in (self.fused_allreduce, self.peer_allreduce):
+            if obj is not None and getattr(obj, "block", None) is not None:
+                status = status or int(obj.status())
+        if status:
+            self.fused_allreduce = None
+            self.peer_allreduce = None
+            from . import twell
+            entry = twell._D2T_LAYERS.get(int(getattr(self.local, "layer_number", -1)))
+            if entry is not None:
+                entry.pop("fused_allreduce", None)
+        return status
+
     def destroy(self) -> None:
         if hasattr(self.local, "destroy"):
             self.local.destroy()
