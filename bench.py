@@ -40,8 +40,15 @@ sys.path.insert(0, str(REPO))
 
 LAYERS, D_MODEL, D_FF = 28, 2048, 8192
 DENSITY, SKEW = 0.02, 1.0
+NCU_DRAM_OVER_ALGORITHMIC = 33.73 / 33.71
 METRIC = "sparse_ffn_decode_tokens_per_s"
 UNIT = "tokens/s"
+
+
+def workload_name(args) -> str:
+    return (f"1.5B-shape sparse FFN stack decode: {args.layers} layers, d_model {args.d_model}, "
+            f"d_ff {args.d_ff}, batch {args.batch}, gate density ~{DENSITY:.0%} "
+            f"log-normal sigma {SKEW}")
 
 
 def parse():
@@ -147,18 +154,26 @@ def shard_range(h: int, rank: int, world: int):
     return start * 256, (start + n) * 256
 
 
+def full_layer_weights(args, device, l):
+    """fp32 [3, d_ff, d_model] (gate, up, down) of layer ``l``, the same on every rank."""
+    from sparser_faster_llms_b200 import synthetic
+    d, h = args.d_model, args.d_ff
+    gen = torch.Generator(device=device).manual_seed(1000 + l)
+    w = torch.randn(3, h, d, generator=gen, device=device, dtype=torch.float32) * 0.02
+    cg = torch.Generator().manual_seed(2000 + l)
+    rates = synthetic.neuron_rates(h, DENSITY, SKEW, cg)
+    shift = (0.02 * (d - 1) ** 0.5 * torch.special.ndtri(rates)).float().to(device)
+    w[0, :, 0] = shift  # bias folded into feature 0 (tokens carry x[:, 0] = 1)
+    return w
+
+
 def build_layers(args, device, rank, world):
     from sparser_faster_llms_b200 import synthetic
     d, h = args.d_model, args.d_ff
     h0, h1 = shard_range(h, rank, world)
     layers = []
     for l in range(args.layers):
-        gen = torch.Generator(device=device).manual_seed(1000 + l)
-        w = torch.randn(3, h, d, generator=gen, device=device, dtype=torch.float32) * 0.02
-        cg = torch.Generator().manual_seed(2000 + l)
-        rates = synthetic.neuron_rates(h, DENSITY, SKEW, cg)
-        shift = (0.02 * (d - 1) ** 0.5 * torch.special.ndtri(rates)).float().to(device)
-        w[0, :, 0] = shift  # bias folded into feature 0 (tokens carry x[:, 0] = 1)
+        w = full_layer_weights(args, device, l)
         wb = w[:, h0:h1].to(torch.bfloat16).contiguous()
         layers.append((wb[0], wb[1], wb[2]))
         del w
@@ -221,7 +236,7 @@ def make_peer_allreduce(args, device, dist_on):
         par = peer_allreduce.PeerAllReduce(args.batch * args.d_model * 2, device=device)
         if args.collective == "fused" and args.batch <= 256:
             far = peer_allreduce.FusedShardAllReduce(args.batch, args.d_model, device=device)
-    except Exception as exc:  # symmetric memory not available on this box
+    except Exception as exc:  # symmetric memory not available on this machine
         why = f"{type(exc).__name__}: {exc}"[:160]
         par = far = None
     ok = torch.tensor([1 if par is not None else 0], device=device)
@@ -352,11 +367,9 @@ def run_ours(args):
     result = {
         "metric": METRIC, "value": B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"1.5B-shape sparse FFN stack decode: {L} layers, d_model {d}, "
-                               f"d_ff {args.d_ff}, batch {B}, gate density ~{DENSITY:.0%} "
-                               f"log-normal sigma {SKEW}",
+        "config": {"workload": workload_name(args),
                    "layers": L, "d_model": d, "d_ff": args.d_ff, "batch": B,
                    "d_ff_shard": [h0, h1], "parallelism": f"dff_shard{world}",
                    "l2": "weights (2.8 GB) exceed L2; no flush needed",
@@ -373,9 +386,9 @@ def run_ours(args):
                      "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": achieved / peak,
-                     # ncu dram__bytes_read+write per launch = 1.00 x the algorithmic bytes
-                     # (profiles/decode_ffn_batch32_pack_and_contraction.md), scaled to this launch
-                     "traffic": float(pack_bytes),
+                     # DRAM bytes per launch: one ncu capture of this kernel at this shape read
+                     # 33.73 MB for 33.71 MB of algorithmic bytes; scaled to this launch
+                     "traffic": float(pack_bytes) * NCU_DRAM_OVER_ALGORITHMIC,
                      "us_per_launch": ms_pack * 1e3, "algorithmic_bytes": pack_bytes},
         "gpu_launches": args.steps * L * (3 if (par is not None and far is None) else 2),
         "clocks": clocks,
@@ -411,6 +424,20 @@ def run_ours(args):
 
     if not args.no_e2e:
         result["e2e"] = run_e2e(args, layers, x, device, dist_on, par)
+    if dist_on and rank == 0:
+        # self-check of the sharded sum: layer 0 recomputed on this rank alone over all of d_ff
+        wf = full_layer_weights(args, device, 0).to(torch.bfloat16).contiguous()
+        packed_f = torch.zeros(B, twell.packed_width(args.d_ff), device=device,
+                               dtype=torch.uint32)
+        y_f = torch.empty(B, d, device=device, dtype=torch.bfloat16)
+        _lib.call("b200_twell_gated_mlp", device, x[0].data_ptr(), wf[0].data_ptr(), None,
+                  wf[1].data_ptr(), wf[2].data_ptr(), packed_f.data_ptr(), y_f.data_ptr(),
+                  B, d, args.d_ff, 8, 0, *ws)
+        torch.cuda.synchronize(device)
+        diff = out[0].float() - y_f.float()
+        result["config"]["max_abs_vs_unsharded"] = float(diff.abs().max())
+        result["config"]["rel_l2_vs_unsharded"] = float(diff.norm() / y_f.float().norm())
+        del wf
     if par is not None:
         # non-zero: a bounded wait on a peer gave up somewhere in the run (results invalid)
         result["config"]["peer_allreduce_status"] = par.status()
@@ -423,6 +450,10 @@ def run_ours(args):
     if dist_on:
         torch.cuda.synchronize(device)
         dist.barrier()
+        if par is not None:
+            par.close()  # no peer mapping is held when the process leaves
+            torch.cuda.synchronize(device)
+            dist.barrier()
         # Tearing the NCCL communicator down while captured graphs still hold its kernels
         # stalled on this stack: every rank has finished and flushed, so leave without the
         # collective teardown.
@@ -481,28 +512,74 @@ def run_e2e(args, layers, x, device, dist_on, par=None):
 # ----------------------------------------------------------------------------
 # CPU legs
 # ----------------------------------------------------------------------------
+def reference_sparse_mlp(d, h):
+    """The reference's own SparseMLP (custom_models/sparse_models.py:259-412) on its torch
+    inference path, from the files staged under oracle/_ref; None where they are absent."""
+    try:
+        from oracle import make_ref
+        if not make_ref.available():
+            return None
+        if make_ref.import_path() not in sys.path:
+            sys.path.insert(0, make_ref.import_path())
+        from custom_models.sparse_models import NullTracker, SparseLlamaConfig, SparseMLP
+        cfg = SparseLlamaConfig(hidden_size=d, intermediate_size=h, num_hidden_layers=1,
+                                num_attention_heads=16, num_key_value_heads=16, vocab_size=64)
+        return SparseMLP(layer_idx=0, config=cfg, gated=True, tracker=NullTracker(1, 1),
+                         execution_logic="inference").eval()
+    except Exception:
+        return None
+
+
 def cpu_baseline(args, sample_layers, reps):
-    """Dense torch formulation of the FFN (the reference's CPU path,
-    sparse_models.py:343-351) on the host cores, bf16 weights, bounded sample."""
+    """The FFN stack on the host cores: the reference's SparseMLP torch path
+    (SparseMLP._forward_mlp_inference_logic, sparse_models.py:343-351) where its files are
+    staged (kind "reference"), else the oracle's dense restatement of it (kind "port").
+    fp32, every host thread, bounded sample scaled to the full stack."""
     from oracle import ffn_oracle as fo
     from sparser_faster_llms_b200 import synthetic
     d, h, B = args.d_model, args.d_ff, args.batch
+    torch.set_num_threads(os.cpu_count() or 1)  # torchrun sets OMP_NUM_THREADS=1
     threads = torch.get_num_threads()
     ffns = [synthetic.make_ffn(d, h, seed=50 + i, density=DENSITY, skew_sigma=SKEW)
             for i in range(sample_layers)]
     x = synthetic.make_tokens(B, d, seed=60)
-    ws = [(f.gate.float(), f.up.float(), f.down.float()) for f in ffns]
+    mlp = reference_sparse_mlp(d, h)
+    if mlp is not None:
+        mods = []
+        import copy
+        for f in ffns:
+            m = copy.deepcopy(mlp)
+            with torch.no_grad():
+                m.gate_proj.weight.copy_(f.gate.float())
+                m.up_proj.weight.copy_(f.up.float())
+                m.down_proj.weight.copy_(f.down.float().T)
+            mods.append(m)
+        xs = x.float().unsqueeze(0)
+
+        def run_layers():
+            with torch.inference_mode():
+                for m in mods:
+                    m(xs)
+        kind = "reference"
+        what = "the reference's SparseMLP torch inference path"
+    else:
+        ws = [(f.gate.float(), f.up.float(), f.down.float()) for f in ffns]
+
+        def run_layers():
+            for g, u, dn in ws:
+                fo.dense_ffn(x, g, u, dn)
+        kind = "port"
+        what = "fp32 torch dense formula (oracle restatement)"
     times = []
     for r in range(reps + 1):
         t0 = time.perf_counter()
-        for g, u, dn in ws:
-            fo.dense_ffn(x, g, u, dn)
+        run_layers()
         times.append(time.perf_counter() - t0)
     per_layer = statistics.median(times[1:]) / sample_layers
     return {"value": B / (per_layer * args.layers), "unit": UNIT, "cores": threads,
-            "kind": "port", "ms_per_step": per_layer * args.layers * 1e3,
-            "sample": f"{sample_layers} of {args.layers} layers at batch {B}, fp32 torch dense "
-                      f"formula, median of {reps} reps, scaled to {args.layers} layers"}
+            "kind": kind, "ms_per_step": per_layer * args.layers * 1e3,
+            "sample": f"{sample_layers} of {args.layers} layers at batch {B}, {what}, fp32, "
+                      f"median of {reps} reps, scaled to {args.layers} layers"}
 
 
 def run_reference(args):
@@ -517,10 +594,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": base["ms_per_step"], "higher_is_better": True,
-        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": f"1.5B-shape sparse FFN stack decode: {args.layers} layers, "
-                               f"d_model {args.d_model}, d_ff {args.d_ff}, batch {args.batch}",
+        "config": {"workload": workload_name(args),
                    "note": "reference CUDA kernels are sm_90a-only (WGMMA) and cannot run on "
                            "sm_100; this arm times the reference's torch CPU formulation"},
         "cpu_baseline": base,

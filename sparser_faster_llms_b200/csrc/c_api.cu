@@ -52,13 +52,18 @@ int twell_decode_status();
 void twell_decode_trace(unsigned long long* out16);
 #endif
 
-// Whether b200_twell_gated_mlp / b200_twell_mlp hand decode-sized calls to the fused one-kernel
-// form when the caller's workspace is large enough (B200_DECODE_FUSED=0 keeps two kernels).
+// Whether b200_twell_gated_mlp / b200_twell_mlp hand decode-sized calls to the one-kernel
+// form when the caller's workspace is large enough.  Off unless B200_DECODE_FUSED=1: measured
+// on B200 (D 2048, H 8192, 28 layers under graph replay) the one-kernel form takes 23.9 / 30.3 /
+// 44.4 us per layer at 1 / 8 / 32 tokens against 17.0 / 20.2 / 25.3 us for pack + contraction -
+// its six phases (split-k exchange, finalise, lists, row staging, cross-tile barrier, sum) each
+// cost 1.5-4 us of latency on one resident CTA per SM, more than the launch and slab round
+// trip they save.
 bool decode_fused_enabled() {
   static int on = -1;
   if (on < 0) {
     const char* e = getenv("B200_DECODE_FUSED");
-    on = (e != nullptr && atoi(e) == 0) ? 0 : 1;
+    on = (e != nullptr && atoi(e) == 1) ? 1 : 0;
   }
   return on != 0;
 }

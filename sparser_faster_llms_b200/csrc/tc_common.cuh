@@ -116,6 +116,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 8 consecutive accumulator columns of this warp's 32 TMEM lanes.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+  uint32_t r[8];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Barrier 2 for `count` threads (count a multiple of 32).
+__device__ __forceinline__ void named_barrier2(int count) {
+  asm volatile("bar.sync 2, %0;" ::"r"(count) : "memory");
+}
+
 __device__ __forceinline__ void epi_barrier() {  // the 128 epilogue threads only
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }

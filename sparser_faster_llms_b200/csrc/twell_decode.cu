@@ -67,15 +67,14 @@ __device__ __forceinline__ void dec_stamp(int i) {
 __device__ __forceinline__ void dec_stamp(int) {}
 #endif
 
-constexpr int kDecThreads = 256;  // warp 0 producer, 1 mma, 2..5 epilogue, 6..7 join from phase 3
+constexpr int kDecThreads = 512;  // warp 0 producer, 1 mma, 2..5 epilogue; all 16 from phase 3
 constexpr int kDecWarps = kDecThreads / 32;
-static_assert(kDecThreads == kTileN, "phase 3 maps one thread to one neuron of the tile");
 constexpr int kDecTok = 32;                   // token rows of the MMA tile (padded)
 constexpr int kDecPartStride = kTileN + 4;    // floats per row of the partial-sum inbox
 constexpr int kDecRingStageBytes = 2 * kATileBytes;  // two 128-neuron halves of a k step
 constexpr int kDecPartBytes = kDecTok * kDecPartStride * 4;
 constexpr int kDecGtileBytes = kDecTok * kTileN * 2;
-constexpr int kDecMaxStageRows = 64;          // active neurons staged per round, at most
+constexpr int kDecMaxBufs = 4;                // staging buffers for up / down row slices
 constexpr uint32_t kDecSpinLimit = 1u << 22;
 
 // Workspace words used by the cross-tile barrier (see twell_t2d.cu for the whole layout).
@@ -99,14 +98,17 @@ __device__ __forceinline__ void dec_fail(int code) { atomicExch(&g_dec_error, co
 // Shared-memory layout of the lists that replace the partial-sum inbox after phase 2.
 template <int CL>
 struct DecLists {
-  static constexpr int kPairMax = 4096 / CL;  // (neuron, token) pairs per round
+  static constexpr int kPairMax = 4096 / CL;  // (neuron, token) pairs per exchange of u
+  static constexpr int kChunkRows = kPairMax / 32 < 32 ? kPairMax / 32 : 32;  // rows per chunk
+  static constexpr int kChunks = kTileN / kChunkRows;
   float uin[CL][kPairMax];                    // slice sums of u, one row per source CTA
   float h[kPairMax];
   unsigned char ptok[kPairMax];               // token of a pair
-  unsigned char prow[kPairMax];               // staged row (slot - round start) of a pair
-  uint32_t mlist[kTileN];                     // token mask of active neuron `slot`
+  unsigned char pslot[kPairMax];              // active slot of a pair - first slot of the exchange
+  uint32_t mlist[kTileN];                     // token mask of active slot
   int poff[kTileN + 1];                       // exclusive prefix of popc(mlist)
   unsigned short nlist[kTileN];               // neuron (inside the tile) of active slot
+  uint32_t rowmask[kChunks][32];              // per chunk and token: rows of the chunk it fires
 };
 static_assert(sizeof(DecLists<4>) <= kDecPartBytes, "lists must fit the inbox they replace");
 static_assert(sizeof(DecLists<8>) <= kDecPartBytes, "lists must fit the inbox they replace");
@@ -122,7 +124,7 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_x, const float* __restrict__ bias,
                     uint32_t* __restrict__ packed, const __nv_bfloat16* __restrict__ up,
                     const __nv_bfloat16* __restrict__ down, __nv_bfloat16* out, int M, int D,
-                    int slab_w, int row_words, int stage_rows, float* ws_part,
+                    int slab_w, int row_words, int nbuf, float* ws_part,
                     unsigned int* ws_sync, const unsigned char* pf_ptr, long long pf_bytes) {
   constexpr int NTOK = kDecTok;
   constexpr int TOK = NTOK / CL;  // tokens finalised by this CTA
@@ -130,15 +132,17 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
   constexpr uint32_t kIdesc = umma_idesc(128, NTOK);
   constexpr int EPT = TOK * kTileN / 128;
   constexpr int PMAX = DecLists<CL>::kPairMax;
+  constexpr int CH = DecLists<CL>::kChunkRows;
   constexpr uint32_t FULL = 0xffffffffu;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar, up_bar, dn_bar;
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar,
+      buf_bar[kDecMaxBufs];
   __shared__ uint32_t tmem_slot;
   __shared__ int cnt_chunk[TOK][8];
-  __shared__ int warp_cnt[kDecWarps];
+  __shared__ int warp_cnt[8];
   __shared__ uint32_t release0_s;
 
   cg::cluster_group cluster = cg::this_cluster();
@@ -160,8 +164,9 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
   DecLists<CL>& L = *reinterpret_cast<DecLists<CL>*>(part);
   // after phase 2 the ring holds the accumulator and the staged weight slices
   float* yacc = reinterpret_cast<float*>(ring);
-  unsigned char* up_s = ring + (((size_t)M * kc * 4 + 1023) & ~(size_t)1023);
-  unsigned char* dn_s = up_s + (size_t)stage_rows * kc * 2;
+  const int row_bytes = kc * 2;
+  const int buf_bytes = CH * row_bytes;
+  unsigned char* stage0 = ring + (((size_t)M * kc * 4 + 1023) & ~(size_t)1023);
 
   if (tid == 0) {
 #pragma unroll
@@ -170,8 +175,8 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&acc_bar, 1);
-    mbar_init(&up_bar, 1);
-    mbar_init(&dn_bar, 1);
+#pragma unroll
+    for (int b = 0; b < kDecMaxBufs; ++b) mbar_init(&buf_bar[b], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     release0_s = reinterpret_cast<volatile unsigned int*>(ws_sync)[2 * crank + 1];
   }
@@ -223,7 +228,7 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
       umma_commit(&acc_bar);
     }
   } else if (warp == 6) {
-    // L2 prefetch of the caller's range (the next layer's gate matrix): this CTA's share
+    // L2 prefetch of the caller's range (e.g. the next layer's gate matrix): this CTA's share
     if (pf_ptr != nullptr && pf_bytes > 0) {
       const long long piece = 16384;
       const long long pieces = (pf_bytes + piece - 1) / piece;
@@ -245,16 +250,17 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
     cluster.barrier_wait();  // B0: every CTA of the cluster is running
     const int nl = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    float v0[32], v1[32];
-    tmem_ld32(lane_addr, v0);
-    tmem_ld32(lane_addr + (uint32_t)NTOK, v1);
 #pragma unroll
-    for (int c = 0; c < NTOK; ++c) {
-      const int owner = c / TOK, tl = c % TOK;
-      float* dst = cluster.map_shared_rank(part, owner) +
-                   (size_t)(crank * TOK + tl) * kDecPartStride + nl;
-      dst[0] = v0[c];
-      dst[128] = v1[c];
+    for (int half = 0; half < 2; ++half) {
+      float v[32];
+      tmem_ld32(lane_addr + (uint32_t)(half * NTOK), v);
+#pragma unroll
+      for (int c = 0; c < NTOK; ++c) {
+        const int owner = c / TOK, tl = c % TOK;
+        float* dst = cluster.map_shared_rank(part, owner) +
+                     (size_t)(crank * TOK + tl) * kDecPartStride + nl + half * 128;
+        dst[0] = v[c];
+      }
     }
   } else {
     cluster.barrier_wait();  // B0 for the other warps
@@ -262,12 +268,6 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   cluster.sync();  // B1: all partials delivered; every CTA's MMAs are complete
   dec_stamp(2);
-  if (warp == 1) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(kTmemCols)
-                 : "memory");
-  }
 
   if (warp >= 2 && warp < 6) {
     // ---- phase 2b: finalise tokens [crank*TOK, (crank+1)*TOK), slab + gate tile ----
@@ -290,6 +290,7 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
       if (lane == 0) cnt_chunk[tl][nl / 32] = __popc(mask[i]);
     }
     epi_barrier();
+    dec_stamp(8);
     if (et < TOK) {
       int run = 0;
 #pragma unroll
@@ -316,6 +317,7 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
       gtile[tok * kTileN + nl] = stored ? (unsigned short)bits : (unsigned short)0;
     }
     epi_barrier();
+    dec_stamp(9);
     // all-gather: this CTA's TOK rows of the gate tile go to the other CTAs of the cluster
     {
       const uint4* src = reinterpret_cast<const uint4*>(gtile + crank * TOK * kTileN);
@@ -327,172 +329,262 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
         for (int i = et; i < kVec; i += 128) dst[i] = src[i];
       }
     }
+    dec_stamp(10);
   } else {
     // the ring is free (B1): clear the accumulator while the epilogue warps finalise
     const int n4 = M * kc / 4;
-    const int t4 = (warp < 2 ? warp : warp - 4) * 32 + lane;  // 0..127 over warps 0, 1, 6, 7
-    for (int i = t4; i < n4; i += 128)
+    const int t4 = (warp < 2 ? warp : warp - 4) * 32 + lane;  // 0..383 over the other 12 warps
+    for (int i = t4; i < n4; i += kDecThreads - 128)
       reinterpret_cast<float4*>(yacc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   cluster.sync();  // B2: gate tile complete in every CTA; inbox no longer read
   dec_stamp(3);
 
   // ---- phase 3: lists (identical in every CTA of the cluster) --------------------------
+  int n_act = 0;
   {
     uint32_t tmask = 0;
+    uint32_t ball = 0;
+    if (tid < kTileN) {
 #pragma unroll 8
-    for (int t = 0; t < NTOK; ++t)
-      if (gtile[t * kTileN + tid] != 0) tmask |= 1u << t;
-    const bool act = tmask != 0;
-    const uint32_t ball = __ballot_sync(FULL, act);
-    if (lane == 0) warp_cnt[warp] = __popc(ball);
+      for (int t = 0; t < NTOK; ++t)
+        if (gtile[t * kTileN + tid] != 0) tmask |= 1u << t;
+      ball = __ballot_sync(FULL, tmask != 0);
+      if (lane == 0) warp_cnt[warp] = __popc(ball);
+    }
     __syncthreads();
-    int base = 0, n_act = 0;
+    int base = 0;
 #pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) {
+    for (int w = 0; w < 8; ++w) {
       const int c = warp_cnt[w];
       if (w < warp) base += c;
       n_act += c;
     }
-    const int slot = base + __popc(ball & lanemask_lt());
-    if (act) {
+    if (tid < kTileN && tmask != 0) {
+      const int slot = base + __popc(ball & lanemask_lt());
       L.nlist[slot] = (unsigned short)tid;
       L.mlist[slot] = tmask;
     }
     __syncthreads();
     // exclusive prefix of the pair counts over the slots (thread = slot)
-    const int c = tid < n_act ? __popc(L.mlist[tid]) : 0;
-    int inc = c;
+    int c = 0, inc = 0;
+    if (tid < kTileN) {
+      c = tid < n_act ? __popc(L.mlist[tid]) : 0;
+      inc = c;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(FULL, inc, o);
-      if (lane >= o) inc += v;
-    }
-    if (lane == 31) warp_cnt[warp] = inc;  // all threads have read warp_cnt above
-    __syncthreads();
-    int wbase = 0;
-#pragma unroll
-    for (int w = 0; w < kDecWarps; ++w)
-      if (w < warp) wbase += warp_cnt[w];
-    L.poff[tid] = wbase + inc - c;
-    if (tid == kDecThreads - 1) L.poff[kTileN] = wbase + inc;
-    __syncthreads();
-
-    // ---- phase 4: contraction, rounds of at most stage_rows active neurons ----
-    const int nrounds = (n_act + stage_rows - 1) / stage_rows;
-    const int row_bytes = kc * 2;
-    const size_t w_row0 = (size_t)tile * kTileN * D + (size_t)k_base;  // element offset
-    auto issue = [&](const __nv_bfloat16* w, unsigned char* dst, uint64_t* bar, int s0, int s1) {
-      // warp 0: one bulk copy per staged row
-      if (warp == 0) {
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)((s1 - s0) * row_bytes));
-        __syncwarp();
-        for (int s = s0 + lane; s < s1; s += 32)
-          bulk_g2s(dst + (size_t)(s - s0) * row_bytes, w + w_row0 + (size_t)L.nlist[s] * D,
-                   (uint32_t)row_bytes, bar);
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(FULL, inc, o);
+        if (lane >= o) inc += v;
       }
-    };
-    if (nrounds > 0) {
-      const int s1 = min(n_act, stage_rows);
-      if (GATED) issue(up, up_s, &up_bar, 0, s1);
-      issue(down, dn_s, &dn_bar, 0, s1);
     }
-    dec_stamp(4);
-    for (int rd = 0; rd < nrounds; ++rd) {
-      const int s0 = rd * stage_rows, s1 = min(n_act, s0 + stage_rows);
-      const int p0 = L.poff[s0], np = L.poff[s1] - p0;
-      const uint32_t par = (uint32_t)rd & 1u;
-      // pair list of the round (thread = staged row)
-      if (tid < s1 - s0) {
-        uint32_t m = L.mlist[s0 + tid];
-        int p = L.poff[s0 + tid] - p0;
+    __syncthreads();  // every thread has read warp_cnt
+    if (tid < kTileN && lane == 31) warp_cnt[warp] = inc;
+    __syncthreads();
+    if (tid < kTileN) {
+      int wbase = 0;
+#pragma unroll
+      for (int w = 0; w < 8; ++w)
+        if (w < warp) wbase += warp_cnt[w];
+      L.poff[tid] = wbase + inc - c;
+      if (tid == kTileN - 1) L.poff[kTileN] = wbase + inc;
+    }
+    // per chunk and token: which rows of the chunk the token fires (one warp per chunk)
+    const int nch_all = (n_act + CH - 1) / CH;
+    for (int ch = warp; ch < nch_all; ch += kDecWarps) {
+      const int s = ch * CH + lane;
+      const uint32_t m = (lane < CH && s < n_act) ? L.mlist[s] : 0u;
+      uint32_t mine = 0;
+#pragma unroll
+      for (int t = 0; t < 32; ++t) {
+        const uint32_t b = __ballot_sync(FULL, (m >> t) & 1u);
+        if (lane == t) mine = b;
+      }
+      L.rowmask[ch][lane] = mine;
+    }
+    __syncthreads();
+  }
+  dec_stamp(4);
+
+  // ---- phase 4: contraction ----------------------------------------------------------------
+  // The active rows are walked in chunks of CH.  An "exchange" is a run of chunks whose pairs
+  // fit the u inbox (normally the whole tile): its up chunks stream through the staging
+  // buffers for pass A, one cluster barrier publishes the slice sums, then its down chunks
+  // stream through the same buffers for pass B.
+  {
+    const int nch = (n_act + CH - 1) / CH;
+    const size_t w_row0 = (size_t)tile * kTileN * D + (size_t)k_base;  // element offset
+    int item_g = 0;   // items issued / consumed so far: buffer = item % nbuf
+    int c0 = 0;
+    bool first_exchange = true;
+    while (c0 < nch) {
+      const int pbase = L.poff[c0 * CH];
+      int c1 = c0 + 1;
+      while (c1 < nch && L.poff[min(n_act, (c1 + 1) * CH)] - pbase <= PMAX) ++c1;
+      const int sA = c0 * CH, sB = min(n_act, c1 * CH);
+      const int np = L.poff[sB] - pbase;
+      const int ncs = c1 - c0;
+      const int nitems = GATED ? 2 * ncs : ncs;
+      // item i of this exchange: up chunk c0 + i (i < ncs, gated) else down chunk
+      auto issue = [&](int i) {
+        if (warp == 0) {
+          const bool is_up = GATED && i < ncs;
+          const int ch = c0 + (is_up ? i : i - (GATED ? ncs : 0));
+          const int s0 = ch * CH, s1 = min(n_act, s0 + CH);
+          const int b = (item_g + i) % nbuf;
+          const __nv_bfloat16* w = is_up ? up : down;
+          unsigned char* dst = stage0 + (size_t)b * buf_bytes;
+          if (lane == 0) mbar_expect_tx(&buf_bar[b], (uint32_t)((s1 - s0) * row_bytes));
+          __syncwarp();
+          for (int s = s0 + lane; s < s1; s += 32)
+            bulk_g2s(dst + (size_t)(s - s0) * row_bytes, w + w_row0 + (size_t)L.nlist[s] * D,
+                     (uint32_t)row_bytes, &buf_bar[b]);
+        }
+      };
+      for (int i = 0; i < nbuf && i < nitems; ++i) issue(i);
+      // pair list of the exchange (thread = slot)
+      for (int s = sA + tid; s < sB; s += kDecThreads) {
+        uint32_t m = L.mlist[s];
+        int p = L.poff[s] - pbase;
         while (m) {
           const int t = __ffs(m) - 1;
           m &= m - 1;
           L.ptok[p] = (unsigned char)t;
-          L.prow[p] = (unsigned char)tid;
+          L.pslot[p] = (unsigned char)(s - sA);
           ++p;
         }
       }
       __syncthreads();
-      if (GATED) {
-        if (!mbar_wait(&up_bar, par)) dec_fail(4);
-        if (rd > 0) cluster.barrier_wait();  // Bb: every CTA has read the previous round's uin
-        // pass A: one warp per pair, this CTA's slice of the dot product
-        for (int p = warp; p < np; p += kDecWarps) {
+      if (!GATED) {  // plain down projection: h is the stored value itself
+        for (int p = tid; p < np; p += kDecThreads) {
           const int t = L.ptok[p];
-          const unsigned char* wrow = up_s + (size_t)L.prow[p] * row_bytes;
-          float s = 0.f;
-          for (int qv = lane; qv < kc / 8; qv += 32) {
-            const uint4 xv = *reinterpret_cast<const uint4*>(
-                xs + (size_t)(qv >> 3) * 4096 + t * 128 + (((qv & 7) ^ (t & 7)) << 4));
-            const uint4 wv = *reinterpret_cast<const uint4*>(wrow + qv * 16);
-            const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
-            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+          const int n = L.nlist[sA + L.pslot[p]];
+          L.h[p] = __bfloat162float(__ushort_as_bfloat16(gtile[t * kTileN + n]));
+        }
+        __syncthreads();
+      }
+      for (int i = 0; i < nitems; ++i) {
+        const int gi = item_g + i;
+        const int b = gi % nbuf;
+        const bool is_up = GATED && i < ncs;
+        const int ch = c0 + (is_up ? i : i - (GATED ? ncs : 0));
+        const int s0 = ch * CH, s1 = min(n_act, s0 + CH);
+        const unsigned char* buf = stage0 + (size_t)b * buf_bytes;
+        if (!mbar_wait(&buf_bar[b], (uint32_t)(gi / nbuf) & 1u)) dec_fail(4);
+        if (is_up) {
+          if (i == 0 && !first_exchange) cluster.barrier_wait();  // Bb: previous uin is read
+          // pass A: 8 lanes per pair, 4 pairs per warp; this CTA's slice of the dot product
+          const int pa = L.poff[s0] - pbase, pb = L.poff[s1] - pbase;
+          const int sub = lane & 7;
+          for (int pw = pa + warp * 4; pw < pb; pw += kDecWarps * 4) {
+            const int p = pw + (lane >> 3);
+            const bool valid = p < pb;
+            const int t = valid ? L.ptok[p] : 0;
+            const int r = valid ? (int)L.pslot[p] - (s0 - sA) : 0;
+            const unsigned char* wrow = buf + (size_t)r * row_bytes + sub * 16;
+            const unsigned char* xrow = xs + t * 128 + ((sub ^ (t & 7)) << 4);
+            float sa = 0.f, sb = 0.f;
+            for (int j = 0; j < ksteps; ++j) {
+              const uint4 xv = *reinterpret_cast<const uint4*>(xrow + (size_t)j * 4096);
+              const uint4 wv = *reinterpret_cast<const uint4*>(wrow + j * 128);
+              const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+              const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              if (HP) {
-                const float2 wf = __bfloat1622float2(w2[e]), xf = __bfloat1622float2(x2[e]);
-                s = __fmaf_rn(wf.x, xf.x, s);
-                s = __fmaf_rn(wf.y, xf.y, s);
-              } else {
-                const float2 pf = __bfloat1622float2(__hmul2(x2[e], w2[e]));
-                s += pf.x;
-                s += pf.y;
+              for (int e = 0; e < 4; ++e) {
+                if (HP) {
+                  const float2 wf = __bfloat1622float2(w2[e]), xf = __bfloat1622float2(x2[e]);
+                  sa = __fmaf_rn(wf.x, xf.x, sa);
+                  sb = __fmaf_rn(wf.y, xf.y, sb);
+                } else {
+                  const float2 pf = __bfloat1622float2(__hmul2(x2[e], w2[e]));
+                  sa += pf.x;
+                  sb += pf.y;
+                }
               }
             }
+            float sum = sa + sb;
+            sum += __shfl_xor_sync(FULL, sum, 4);
+            sum += __shfl_xor_sync(FULL, sum, 2);
+            sum += __shfl_xor_sync(FULL, sum, 1);
+            if (valid && sub < CL)
+              cluster.map_shared_rank(&L.uin[0][0], sub)[crank * PMAX + p] = sum;
           }
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FULL, s, o);
-          if (lane < CL) cluster.map_shared_rank(&L.uin[0][0], lane)[crank * PMAX + p] = s;
-        }
-        cluster.sync();  // Ba: the round's slice sums are in every CTA; up_s is free
-        if (rd + 1 < nrounds) issue(up, up_s, &up_bar, s1, min(n_act, s1 + stage_rows));
-      }
-      // h of every pair of the round
-      for (int p = tid; p < np; p += kDecThreads) {
-        const int t = L.ptok[p];
-        const int n = L.nlist[s0 + L.prow[p]];
-        const __nv_bfloat16 g = __ushort_as_bfloat16(gtile[t * kTileN + n]);
-        float hv;
-        if (GATED) {
-          float u = 0.f;
-#pragma unroll
-          for (int r = 0; r < CL; ++r) u += L.uin[r][p];
-          hv = HP ? __bfloat162float(g) * u
-                  : __bfloat162float(__hmul(g, __float2bfloat16_rn(u)));
         } else {
-          hv = __bfloat162float(g);
-        }
-        L.h[p] = hv;
-      }
-      __syncthreads();
-      if (GATED && rd + 1 < nrounds) cluster.barrier_arrive();  // Bb: uin of this round is read
-      if (!mbar_wait(&dn_bar, par)) dec_fail(5);
-      // pass B: y[t, slice] += h * down[n, slice]; a thread owns fixed column pairs
-      for (int p = 0; p < np; ++p) {
-        const int t = L.ptok[p];
-        const float hv = L.h[p];
-        const __nv_bfloat162* drow =
-            reinterpret_cast<const __nv_bfloat162*>(dn_s + (size_t)L.prow[p] * row_bytes);
-        float2* yrow = reinterpret_cast<float2*>(yacc + (size_t)t * kc);
-        const __nv_bfloat162 hb2 = __float2bfloat162_rn(hv);
-        for (int c2 = tid; c2 < kc / 2; c2 += kDecThreads) {
-          float2 y = yrow[c2];
-          if (HP) {
-            const float2 wf = __bfloat1622float2(drow[c2]);
-            y.x = __fmaf_rn(wf.x, hv, y.x);
-            y.y = __fmaf_rn(wf.y, hv, y.y);
-          } else {
-            const float2 pf = __bfloat1622float2(__hmul2(hb2, drow[c2]));
-            y.x += pf.x;
-            y.y += pf.y;
+          // pass B: token-major inside the chunk.  A group of kc / 8 threads owns one token at
+          // a time (thread = 8 columns): y[t, cols] += h * down[row, cols] for the rows the
+          // token fires, then the next token of the group.
+          const int tpg = kc / 8;                    // threads per group
+          const int groups = kDecThreads / tpg;
+          const int g = tid / tpg, cl8 = (tid - g * tpg) * 8;
+          if (g < groups) {
+            for (int t = g; t < M; t += groups) {
+              uint32_t m = L.rowmask[ch][t];
+              if (m == 0) continue;
+              float* yrow = yacc + (size_t)t * kc + cl8;
+              float4 y0 = *reinterpret_cast<const float4*>(yrow);
+              float4 y1 = *reinterpret_cast<const float4*>(yrow + 4);
+              const uint32_t below = (1u << t) - 1u;
+              while (m) {
+                const int r = __ffs(m) - 1;
+                m &= m - 1;
+                const int s = s0 + r;
+                const int p = L.poff[s] - pbase + __popc(L.mlist[s] & below);
+                const float hv = L.h[p];
+                const uint4 wv = *reinterpret_cast<const uint4*>(buf + (size_t)r * row_bytes +
+                                                                 cl8 * 2);
+                const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+                if (HP) {
+                  const float2 a = __bfloat1622float2(w2[0]), bq = __bfloat1622float2(w2[1]),
+                               cq = __bfloat1622float2(w2[2]), dq = __bfloat1622float2(w2[3]);
+                  y0.x = __fmaf_rn(a.x, hv, y0.x);
+                  y0.y = __fmaf_rn(a.y, hv, y0.y);
+                  y0.z = __fmaf_rn(bq.x, hv, y0.z);
+                  y0.w = __fmaf_rn(bq.y, hv, y0.w);
+                  y1.x = __fmaf_rn(cq.x, hv, y1.x);
+                  y1.y = __fmaf_rn(cq.y, hv, y1.y);
+                  y1.z = __fmaf_rn(dq.x, hv, y1.z);
+                  y1.w = __fmaf_rn(dq.y, hv, y1.w);
+                } else {
+                  const __nv_bfloat162 hb2 = __float2bfloat162_rn(hv);  // h is bf16-representable
+                  const float2 a = __bfloat1622float2(__hmul2(hb2, w2[0])),
+                               bq = __bfloat1622float2(__hmul2(hb2, w2[1])),
+                               cq = __bfloat1622float2(__hmul2(hb2, w2[2])),
+                               dq = __bfloat1622float2(__hmul2(hb2, w2[3]));
+                  y0.x += a.x;
+                  y0.y += a.y;
+                  y0.z += bq.x;
+                  y0.w += bq.y;
+                  y1.x += cq.x;
+                  y1.y += cq.y;
+                  y1.z += dq.x;
+                  y1.w += dq.y;
+                }
+              }
+              *reinterpret_cast<float4*>(yrow) = y0;
+              *reinterpret_cast<float4*>(yrow + 4) = y1;
+            }
           }
-          yrow[c2] = y;
+        }
+        __syncthreads();  // the buffer is free
+        if (i + nbuf < nitems) issue(i + nbuf);
+        if (GATED && i == ncs - 1) {
+          cluster.sync();  // Ba: the slice sums of the exchange are in every CTA
+          for (int p = tid; p < np; p += kDecThreads) {
+            const int t = L.ptok[p];
+            const int n = L.nlist[sA + L.pslot[p]];
+            const __nv_bfloat16 gv = __ushort_as_bfloat16(gtile[t * kTileN + n]);
+            float u = 0.f;
+#pragma unroll
+            for (int r = 0; r < CL; ++r) u += L.uin[r][p];
+            L.h[p] = HP ? __bfloat162float(gv) * u
+                        : __bfloat162float(__hmul(gv, __float2bfloat16_rn(u)));
+          }
+          __syncthreads();
+          if (c1 < nch) cluster.barrier_arrive();  // Bb: this exchange's uin has been read
         }
       }
-      __syncthreads();  // dn_s and the pair list are free
-      if (rd + 1 < nrounds) issue(down, dn_s, &dn_bar, s1, min(n_act, s1 + stage_rows));
+      item_g += nitems;
+      c0 = c1;
+      first_exchange = false;
     }
   }
   dec_stamp(5);
@@ -525,24 +617,46 @@ twell_decode_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
     __syncthreads();
     dec_stamp(6);
-    const int n2 = M * kc / 2, kc2 = kc / 2;
-    const int per = (n2 + tiles - 1) / tiles;
-    const int lo = tile * per, hi = min(n2, lo + per);
+    const int per = (n4 + tiles - 1) / tiles;
+    const int lo = tile * per, hi = min(n4, lo + per);
     for (int i = lo + tid; i < hi; i += kDecThreads) {
-      const int t = i / kc2, c2 = i - t * kc2;
-      const float* src = ws_part + (size_t)t * D + k_base + 2 * c2;
-      float s0 = 0.f, s1 = 0.f;
-#pragma unroll 8
-      for (int q = 0; q < tiles; ++q) {
-        const float2 v = __ldcg(reinterpret_cast<const float2*>(src + (size_t)q * M * D));
-        s0 += v.x;
-        s1 += v.y;
+      const int t = i / kc4, c4 = i - t * kc4;
+      const float4* src = reinterpret_cast<const float4*>(ws_part + (size_t)t * D + k_base) + c4;
+      const size_t qstride = (size_t)M * D / 4;
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      int q = 0;
+      for (; q + 16 <= tiles; q += 16) {
+        float4 v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __ldcg(src + (size_t)(q + j) * qstride);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          s.x += v[j].x;
+          s.y += v[j].y;
+          s.z += v[j].z;
+          s.w += v[j].w;
+        }
       }
-      *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * D + k_base + 2 * c2) =
-          __floats2bfloat162_rn(s0, s1);
+      for (; q < tiles; ++q) {
+        const float4 v = __ldcg(src + (size_t)q * qstride);
+        s.x += v.x;
+        s.y += v.y;
+        s.z += v.z;
+        s.w += v.w;
+      }
+      __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * D + k_base + 4 * c4);
+      o[0] = __floats2bfloat162_rn(s.x, s.y);
+      o[1] = __floats2bfloat162_rn(s.z, s.w);
     }
   }
   dec_stamp(7);
+  // TMEM is released last: nothing above waits for it.
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
 }
 
 // L2 prefetch of an arbitrary byte range (one bulk prefetch per 16 KB piece).
@@ -559,7 +673,7 @@ __global__ void l2_prefetch_kernel(const unsigned char* p, long long bytes) {
 
 // ---- host side -------------------------------------------------------------------------
 struct DecShape {
-  int cl, stages, stage_rows;
+  int cl, stages, nbuf;
   size_t smem;
 };
 
@@ -571,20 +685,20 @@ bool dec_shape(int64_t M, int64_t D, int64_t H, DecShape* s) {
   const int tiles = (int)(H / kTileN);
   if (tiles < 1 || tiles > 255) return false;
   int cl = 4;
-  if (tiles <= 16 && D % 512 == 0) cl = 8;  // a narrow d_ff shard: more CTAs per tile
+  if (tiles <= 8 && D % 512 == 0) cl = 8;  // a narrow d_ff shard: more CTAs per tile
   if (D % (cl * kStageK)) return false;
   const int kc = (int)(D / cl);
+  if (kDecThreads % (kc / 8)) return false;  // pass B: groups of kc / 8 threads
+  const int chunk_rows = (4096 / cl) / 32 < 32 ? (4096 / cl) / 32 : 32;
   const size_t ring = (size_t)kDecStages * kDecRingStageBytes;
   const size_t yacc = ((size_t)M * kc * 4 + 1023) & ~(size_t)1023;
-  if (yacc + 4 * (size_t)kc * 4 > ring) return false;
-  int rows = (int)((ring - yacc) / ((size_t)kc * 4));  // up slice + down slice per row
-  const int by_pairs = (4096 / cl) / (int)M;
-  if (rows > by_pairs) rows = by_pairs;
-  if (rows > kDecMaxStageRows) rows = kDecMaxStageRows;
-  if (rows < 4) return false;
+  const size_t buf = (size_t)chunk_rows * kc * 2;
+  if (yacc + 2 * buf > ring) return false;
+  int nbuf = (int)((ring - yacc) / buf);
+  if (nbuf > kDecMaxBufs) nbuf = kDecMaxBufs;
   s->cl = cl;
   s->stages = kDecStages;
-  s->stage_rows = rows;
+  s->nbuf = nbuf;
   s->smem = ring + (size_t)(kc / kStageK) * 4096 + kDecPartBytes + kDecGtileBytes + 1024;
   return s->smem <= 227 * 1024;
 }
@@ -638,7 +752,7 @@ int launch_decode(const DecShape& shp, const void* x, const void* gate, const fl
       &cfg, kern, map_w, map_x, bias, static_cast<uint32_t*>(packed),
       reinterpret_cast<const __nv_bfloat16*>(up), reinterpret_cast<const __nv_bfloat16*>(down),
       reinterpret_cast<__nv_bfloat16*>(out), (int)M, (int)D, slab_w, tiles * slab_w,
-      shp.stage_rows, ws_part, words + kDecSyncWord0,
+      shp.nbuf, ws_part, words + kDecSyncWord0,
       static_cast<const unsigned char*>(pf_ptr), (long long)pf_bytes);
   if (e != cudaSuccess)
     return fail(B200_ECUDA, "b200_twell_gated_mlp (decode): launch: %s", cudaGetErrorString(e));

@@ -25,6 +25,8 @@
 // shared-memory atomics in the epilogue -> ballot/popc.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "tc_common.cuh"
 
 namespace cg = cooperative_groups;
@@ -394,6 +396,203 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
+// ---------------------------------------------------------------------------
+// The same split-k kernel with sixteen epilogue warps instead of four.  The epilogue of the
+// four-warp form is a latency chain on one warp per scheduler (TMEM read, 64 remote stores
+// per thread, then 16 elements per thread to sum, ballot and store).  Here four groups of
+// four warps each read 8 token columns of their TMEM lane quarter (tcgen05.ld ...x8) and push
+// 16 values per thread, and all 512 epilogue threads take part in the final pass (4 elements
+// per thread for a 4-CTA cluster).  Same arithmetic, same slab bytes.
+// Threads: warp 0 producer, warp 1 mma, warps 2..17 epilogue (group = (warp - 2) / 4, TMEM
+// lane quarter = warp % 4).
+// ---------------------------------------------------------------------------
+constexpr int kThreadsTcWide = 64 + 512;
+
+template <int CL, int STAGES>
+__global__ void __launch_bounds__(kThreadsTcWide, 1)
+twell_pack_tc_splitk_wide_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                                 const __grid_constant__ CUtensorMap tmap_x,
+                                 const float* __restrict__ bias, uint32_t* __restrict__ packed,
+                                 int M, int D, int slab_w, int row_words) {
+  constexpr int NTOK = kTokDecode;
+  constexpr int TOK = NTOK / CL;
+  constexpr int kBTileBytes = NTOK * 128;
+  constexpr int kStageBytes = 2 * kATileBytes + kBTileBytes;
+  constexpr uint32_t kTmemCols = 2 * NTOK;
+  constexpr uint32_t kIdesc = umma_idesc(128, NTOK);
+  constexpr int EPT = TOK * kTileN / 512;  // elements per epilogue thread in the final pass
+  static_assert(EPT >= 1, "the final pass needs at least one element per thread");
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* part = reinterpret_cast<float*>(smem + (size_t)STAGES * kStageBytes);
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_s;
+  __shared__ int cnt_chunk[TOK][8];
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int crank = (int)cluster.block_rank();
+  cluster.barrier_arrive();  // matched by barrier_wait() before the first remote store
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / CL;
+  const int m0 = blockIdx.y * NTOK;
+  const int kc = D / CL;
+  const int ksteps = kc / kStageK;
+  const int k_base = crank * kc;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+          abort_s = 1;
+          atomicExch(&g_tc_error, 1);
+          break;
+        }
+        unsigned char* st = smem + (size_t)s * kStageBytes;
+        mbar_expect_tx(&full_bar[s], (uint32_t)kStageBytes);
+        const int kcoord = k_base + k * kStageK;
+        tma_load_2d(st, &tmap_w, kcoord, tile * kTileN, &full_bar[s]);
+        tma_load_2d(st + kATileBytes, &tmap_w, kcoord, tile * kTileN + 128, &full_bar[s]);
+        tma_load_2d(st + 2 * kATileBytes, &tmap_x, kcoord, m0, &full_bar[s]);
+      }
+      pdl_launch_dependents();
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], phase)) {
+          abort_s = 1;
+          atomicExch(&g_tc_error, 2);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(smem + (size_t)s * kStageBytes);
+        const uint64_t da0 = umma_desc(a0), da1 = umma_desc(a0 + kATileBytes),
+                       db = umma_desc(a0 + 2 * kATileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kStageK / 16; ++kk) {
+          const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, da0 + 2 * kk, db + 2 * kk, kIdesc, acc);
+          umma_bf16(tmem_base + NTOK, da1 + 2 * kk, db + 2 * kk, kIdesc, acc);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (!abort_s) umma_commit(&acc_bar);
+    }
+  } else {
+    // ---- epilogue part 1: TMEM -> registers -> owner CTA's shared memory ----
+    const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;  // token columns [8 * grp, 8 * grp + 8)
+    bool ok = mbar_wait(&acc_bar, 0u);
+    if (!ok) {
+      abort_s = 1;
+      atomicExch(&g_tc_error, 3);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    cluster.barrier_wait();  // every CTA of the cluster is running
+    if (ok) {
+      const int nl = q * 32 + lane;  // neuron inside the tile (accumulator 0); +128 for 1
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(grp * 8);
+      float v0[8], v1[8];
+      tmem_ld8(lane_addr, v0);
+      tmem_ld8(lane_addr + (uint32_t)NTOK, v1);
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8) {
+        const int c = grp * 8 + c8;
+        const int owner = c / TOK, tl = c % TOK;
+        float* dst = cluster.map_shared_rank(part, owner) +
+                     (size_t)(crank * TOK + tl) * kPartStrideTc + nl;
+        dst[0] = v0[c8];
+        dst[128] = v1[c8];
+      }
+    }
+  }
+  if (warp < 2) cluster.barrier_wait();  // pair the early arrive for the non-epilogue warps
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  cluster.sync();  // all partials delivered (every thread of every CTA takes part)
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+  if (warp < 2 || abort_s) return;
+
+  // ---- epilogue part 2: this CTA finalises tokens [crank*TOK, (crank+1)*TOK) ----
+  const int et = threadIdx.x - 64;  // 0..511
+  const int neuron0 = tile * kTileN;
+  float z[EPT];
+  uint32_t mask[EPT];
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int e = et + i * 512;
+    const int tl = e / kTileN, nl = e % kTileN;
+    const int tok = crank * TOK + tl;
+    float v = 0.f;
+#pragma unroll
+    for (int r = 0; r < CL; ++r) v += part[(size_t)(r * TOK + tl) * kPartStrideTc + nl];
+    if (bias != nullptr) v += bias[neuron0 + nl];
+    const bool keep = (v > 0.f) && (m0 + tok < M);
+    z[i] = v;
+    mask[i] = __ballot_sync(0xffffffffu, keep);
+    if (lane == 0) cnt_chunk[tl][nl / 32] = __popc(mask[i]);
+  }
+  named_barrier2(512);
+  if (et < TOK) {  // counts -> exclusive prefix over the 8 chunks of this token, count word
+    int run = 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int v = cnt_chunk[et][c];
+      cnt_chunk[et][c] = run;
+      run += v;
+    }
+    const int tok = m0 + crank * TOK + et;
+    if (tok < M) packed[(size_t)tok * row_words + (size_t)tile * slab_w] = (uint32_t)run;
+  }
+  named_barrier2(512);
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int e = et + i * 512;
+    const int tl = e / kTileN, nl = e % kTileN;
+    const int tok = crank * TOK + tl;
+    if (m0 + tok >= M) continue;
+    uint32_t* slab = packed + (size_t)(m0 + tok) * row_words + (size_t)tile * slab_w;
+    const int slot = cnt_chunk[tl][nl / 32] + __popc(mask[i] & lanemask_lt());
+    if (((mask[i] >> lane) & 1u) && slot < slab_w - 1)
+      slab[1 + slot] = (uint32_t)(neuron0 + nl) | (bf16_bits(z[i]) << 16);
+  }
+}
+
 // ---- host side -------------------------------------------------------------
 template <int NTOK, int STAGES, int MINB = 1>
 int launch_tc(const void* x, const void* w, const float* bias, void* packed, int64_t M, int64_t D,
@@ -413,22 +612,33 @@ int launch_tc(const void* x, const void* w, const float* bias, void* packed, int
   return check_launch("b200_twell_pack (tcgen05)");
 }
 
-template <int CL, int STAGES>
-int launch_tc_splitk(const void* x, const void* w, const float* bias, void* packed, int64_t M,
-                     int64_t D, int64_t H, int cf, cudaStream_t stream) {
+// Epilogue form of the split-k kernel: sixteen epilogue warps unless B200_PACK_WIDE=0.
+bool pack_wide_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("B200_PACK_WIDE");
+    on = (e != nullptr && atoi(e) == 0) ? 0 : 1;
+  }
+  return on != 0;
+}
+
+template <int CL, int STAGES, bool WIDE>
+int launch_tc_splitk_form(const void* x, const void* w, const float* bias, void* packed,
+                          int64_t M, int64_t D, int64_t H, int cf, cudaStream_t stream) {
   CUtensorMap map_w, map_x;
   if (int rc = make_map(&map_w, w, H, D, 128)) return rc;
   if (int rc = make_map(&map_x, x, M, D, kTokDecode)) return rc;
   const size_t smem = (size_t)STAGES * (2 * kATileBytes + kTokDecode * 128) +
                       (size_t)kTokDecode * kPartStrideTc * sizeof(float) + 1024;
-  auto kern = twell_pack_tc_splitk_kernel<CL, STAGES>;
+  auto kern = WIDE ? twell_pack_tc_splitk_wide_kernel<CL, STAGES>
+                   : twell_pack_tc_splitk_kernel<CL, STAGES>;
   static size_t granted[64] = {0};
   if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_pack")) return rc;
   const int slab_w = kTileN / cf;
   const int tiles = (int)(H / kTileN);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(tiles * CL), (unsigned)((M + kTokDecode - 1) / kTokDecode), 1);
-  cfg.blockDim = dim3(kThreadsTc, 1, 1);
+  cfg.blockDim = dim3(WIDE ? kThreadsTcWide : kThreadsTc, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -445,6 +655,14 @@ int launch_tc_splitk(const void* x, const void* w, const float* bias, void* pack
     return fail(B200_ECUDA, "b200_twell_pack (tcgen05 split-k): launch: %s",
                 cudaGetErrorString(e));
   return B200_OK;
+}
+
+template <int CL, int STAGES>
+int launch_tc_splitk(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                     int64_t D, int64_t H, int cf, cudaStream_t stream) {
+  return pack_wide_enabled()
+             ? launch_tc_splitk_form<CL, STAGES, true>(x, w, bias, packed, M, D, H, cf, stream)
+             : launch_tc_splitk_form<CL, STAGES, false>(x, w, bias, packed, M, D, H, cf, stream);
 }
 
 }  // namespace

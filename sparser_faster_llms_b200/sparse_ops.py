@@ -25,6 +25,18 @@ Registered operators (same names and argument order as custom_op.cpp:308-342, :4
 P, R, T are returned as int32 tensors (a Python-registered operator cannot return a
 TorchScript custom class); :class:`HybridSp` wraps one of them for callers that want
 ``overflow_count_tensor()``.  There is no CPU implementation.
+
+Dense tail (custom_op.cpp:79-116, hybrid_sp.cu:516-576, :811-952, :1358-1383).  A token row
+with more positives in some 256-neuron tile than a slab holds cannot be represented by the
+slabs alone.  With ``discard_overflow == 0`` (the default, as in the reference) up to
+``tail_rows_regular`` such rows are taken out of the sparse kernels - the sign bit of their
+count words is set, which every kernel reads as "no entries" while the true counts stay in
+the low bits - and computed exactly as dense bf16 GEMMs over the gathered rows, forward and
+backward, the way the reference multiplies its ``tail_dense`` rows with ``torch::matmul``.
+The row list is rebuilt from the flags in backward, so nothing but P carries it; no host
+synchronisation is involved (the reference waits on an event per backward).  Rows beyond the
+capacity keep the slab prefix and are counted in ``dropped``.  ``discard_overflow == 1`` keeps
+every row on the slabs: entries past a tile's capacity are dropped and counted.
 """
 from __future__ import annotations
 
@@ -54,6 +66,9 @@ _CONFIG = {
     # weight gradients dK / dG / dV: "sparse" = column lists + transposed SpMM, "dense" =
     # scatter to a K-major matrix + tcgen05 GEMM, "auto" = dense from 2048 tokens on
     "weight_gradient_mode": "auto",
+    # size the tail from the overflow count observed on earlier calls instead of always
+    # computing tail_rows_regular rows (see set_tail_rows_adaptive)
+    "tail_rows_adaptive": 0,
 }
 _LAST_TRANSPOSE_OVERFLOW: torch.Tensor | None = None
 _PERF: dict[str, list[float]] = {}
@@ -91,6 +106,70 @@ def _wgrad_workspace(dev: torch.device, m: int, d: int, h: int) -> torch.Tensor:
         buf = torch.empty(need, dtype=torch.uint8, device=dev)
         _WGRAD_WS[key] = buf
     return buf
+
+
+def set_tail_rows_adaptive(on: bool) -> None:
+    """Size the dense tail from the overflow-row count seen on earlier calls with the same
+    gate matrix (read back asynchronously, never waited for): twice the last count, at least
+    128 rows, at most ``tail_rows_regular``.  Off (the default) the tail always spans
+    ``min(tail_rows_regular, tokens)`` rows, which is what the reference's forward computes
+    (custom_op.cpp:125-127 sets the active rows to the capacity).  With a sudden jump in
+    overflow rows the excess rows of that one call fall back to the slab prefix and are
+    counted in ``dropped``.  No reference counterpart."""
+    _CONFIG["tail_rows_adaptive"] = 1 if on else 0
+
+
+_INT_MIN = -(2 ** 31)
+_TAIL_SEEN: dict[tuple, dict] = {}
+
+
+def _tail_state(key: tuple) -> dict:
+    st = _TAIL_SEEN.get(key)
+    if st is None:
+        if len(_TAIL_SEEN) > 512:
+            _TAIL_SEEN.clear()
+        st = {"host": torch.zeros((), dtype=torch.int64).pin_memory(),
+              "event": None, "last": None, "cap_fwd": 0}
+        _TAIL_SEEN[key] = st
+    return st
+
+
+def _tail_capacity(key: tuple, m: int) -> int:
+    """Rows the forward's dense tail spans for this call (0 = no tail)."""
+    cap = min(int(_CONFIG["tail_rows_regular"]), m)
+    if cap <= 0 or _CONFIG["discard_overflow"]:
+        return 0
+    if not _CONFIG["tail_rows_adaptive"]:
+        return cap
+    st = _tail_state(key)
+    if st["event"] is not None and st["event"].query():
+        st["last"] = int(st["host"].item())
+    if st["last"] is not None:
+        cap = min(cap, max(128, (2 * st["last"] + 127) // 128 * 128))
+    st["cap_fwd"] = max(st["cap_fwd"], cap)  # the backward must span at least this many rows
+    return cap
+
+
+def _tail_observe(key: tuple, n_over: torch.Tensor) -> None:
+    """Start an asynchronous read-back of this call's overflow-row count (never waited for)."""
+    st = _tail_state(key)
+    if st["event"] is not None and not st["event"].query():
+        return  # the previous read-back is still in flight: keep it
+    st["host"].copy_(n_over, non_blocking=True)
+    st["event"] = torch.cuda.Event()
+    st["event"].record()
+
+
+def _count_view(P: torch.Tensor, m: int, h: int, cf: int) -> torch.Tensor:
+    """Strided int32 view ``[m, tiles]`` of the count words of a slab array."""
+    return P.view(m, h // TILE, TILE // cf)[:, :, 0]
+
+
+def _tail_index(in_tail: torch.Tensor, cap: int, m: int):
+    """(idx [cap] clamped to valid rows, valid [cap] bool, scatter index with m = padding)."""
+    raw = torch.nonzero_static(in_tail, size=cap, fill_value=m).reshape(cap)
+    valid = raw < m
+    return raw.clamp(max=max(m - 1, 0)), valid, raw
 
 
 def compression_factor() -> int:
@@ -161,9 +240,11 @@ def _slab_shape(m: int, h: int, cf: int) -> tuple[int, int]:
     return m, (h // TILE) * (TILE // cf)
 
 
-def _spmm(vals: torch.Tensor, B: torch.Tensor, m: int, d: int, h: int, cf: int) -> torch.Tensor:
-    """Row product ``out[r,:] = sum value * B[col,:]`` (fp32 fma, bf16 store)."""
-    out = torch.empty((m, d), dtype=torch.bfloat16, device=vals.device)
+def _spmm(vals: torch.Tensor, B: torch.Tensor, m: int, d: int, h: int, cf: int,
+          pad_rows: int = 0) -> torch.Tensor:
+    """Row product ``out[r,:] = sum value * B[col,:]`` (fp32 fma, bf16 store).  ``pad_rows``
+    extra rows are allocated behind the result (scatter target of the tail's padding index)."""
+    out = torch.empty((m + pad_rows, d), dtype=torch.bfloat16, device=vals.device)
     _lib.call("b200_hybrid_spmm", vals.device, vals.data_ptr(), B.data_ptr(), out.data_ptr(),
               m, d, h, cf, *_lib.workspace(vals.device))
     return out
@@ -179,11 +260,25 @@ def ff_forward_impl(X: torch.Tensor, G: torch.Tensor, K: torch.Tensor, V: torch.
     Xf = X.reshape(m, d).contiguous()
     G, K, V = G.contiguous(), K.contiguous(), V.contiguous()
     shape = _slab_shape(m, h, cf)
+    tail_key = (dev.index, G.data_ptr(), m, h)
+    cap = _tail_capacity(tail_key, m) if m > 0 else 0
     with _Timer("ff_forward_gated_total"):
         P = torch.empty(shape, dtype=torch.int32, device=dev)
         with _Timer("gate_gemm_pack"):
             _lib.call("b200_twell_pack", dev, Xf.data_ptr(), G.data_ptr(), None, P.data_ptr(),
                       m, d, h, cf)
+        inv_m = 1.0 / max(m, 1)
+        tail = None
+        if cap > 0:
+            # rows with an overflowed tile leave the slabs: flag their count words
+            cnt = _count_view(P, m, h, cf)
+            over = (cnt > TILE // cf - 1).any(dim=1)
+            in_tail = over & (over.cumsum(0) <= cap) if cap < m else over
+            l0 = cnt.sum(dtype=torch.float32) * inv_m
+            cnt.bitwise_or_(in_tail.to(torch.int32).mul_(_INT_MIN).unsqueeze(1))
+            tail = _tail_index(in_tail, cap, m)
+            if _CONFIG["tail_rows_adaptive"]:
+                _tail_observe(tail_key, over.sum())
         R = torch.empty_like(P)
         T = torch.empty_like(P)
         row_l1 = torch.empty(m, dtype=torch.float32, device=dev)
@@ -194,10 +289,20 @@ def ff_forward_impl(X: torch.Tensor, G: torch.Tensor, K: torch.Tensor, V: torch.
                       R.data_ptr(), T.data_ptr(), row_l1.data_ptr(), row_nnz.data_ptr(),
                       row_drop.data_ptr(), m, d, h, cf)
         with _Timer("spmm_out"):
-            out = _spmm(T, V, m, d, h, cf)
-        inv_m = 1.0 / max(m, 1)
-        l0 = row_nnz.sum(dtype=torch.float32) * inv_m
-        l1 = row_l1.sum() * inv_m
+            out = _spmm(T, V, m, d, h, cf, pad_rows=1 if tail is not None else 0)
+        l1 = row_l1.sum()
+        if tail is None:
+            l0 = row_nnz.sum(dtype=torch.float32) * inv_m
+        else:
+            with _Timer("dense_tail_forward"):
+                idx, valid, scatter = tail
+                Xt = Xf[idx] * valid.unsqueeze(1)
+                Pt = torch.relu(Xt @ G.t())
+                Tt = (Xt @ K.t()) * Pt
+                out.index_copy_(0, scatter, Tt @ V)
+                l1 = l1 + Tt.abs().sum(dtype=torch.float32)
+            out = out[:m]
+        l1 = l1 * inv_m
         dropped = row_drop.sum(dtype=torch.int32)
     return out.reshape(X.shape), l0, l1, P, R, T, dropped
 
@@ -238,6 +343,18 @@ def ff_backward_impl(X, G, K, V, P, R, T, gR, gl0, gl1):
     gl1_dev = None
     if gl1 is not None:
         gl1_dev = gl1.detach().to(device=dev, dtype=torch.float32).reshape(1).contiguous()
+    # tail rows: flagged count words (sign bit) in P, set by the forward
+    tail = None
+    if m > 0 and not _CONFIG["discard_overflow"] and _CONFIG["tail_rows_regular"] > 0:
+        cap = min(int(_CONFIG["tail_rows_regular"]), m)
+        if _CONFIG["tail_rows_adaptive"]:
+            st = _TAIL_SEEN.get((dev.index, G.data_ptr(), m, h))
+            if st is not None and st["cap_fwd"] > 0:
+                cap = min(cap, st["cap_fwd"])  # what the forward(s) since the last backward used
+                st["cap_fwd"] = 0
+        flagged = (_count_view(P, m, h, cf) < 0).any(dim=1)
+        tail = _tail_index(flagged, cap, m)
+    pad = 1 if tail is not None else 0
     with _Timer("ff_backward_gated_total"):
         dR = torch.empty_like(P)
         dU = torch.empty_like(P)
@@ -245,12 +362,12 @@ def ff_backward_impl(X, G, K, V, P, R, T, gR, gl0, gl1):
             _lib.call("b200_hybrid_sddmm_bwd", dev, gRf.data_ptr(), V.data_ptr(), P.data_ptr(),
                       R.data_ptr(), dR.data_ptr(), dU.data_ptr(), _lib.ptr(gl1_dev), m, d, h, cf)
         with _Timer("spmm_dX"):
-            dX = _spmm(dR, K, m, d, h, cf) + _spmm(dU, G, m, d, h, cf)
+            dX = _spmm(dR, K, m, d, h, cf, pad) + _spmm(dU, G, m, d, h, cf, pad)
+        dK = torch.empty((h, d), dtype=torch.bfloat16, device=dev)
+        dG = torch.empty_like(dK)
+        dV = torch.empty_like(dK)
         if _dense_weight_gradients(m):
             ws = _wgrad_workspace(dev, m, d, h)
-            dK = torch.empty((h, d), dtype=torch.bfloat16, device=dev)
-            dG = torch.empty_like(dK)
-            dV = torch.empty_like(dK)
             with _Timer("wgrad_dense_dK_dG"):
                 _lib.call("b200_hybrid_wgrad_dense", dev, dR.data_ptr(), Xf.data_ptr(),
                           dK.data_ptr(), m, d, h, cf, 0, ws.data_ptr(), ws.numel())
@@ -260,25 +377,42 @@ def ff_backward_impl(X, G, K, V, P, R, T, gR, gl0, gl1):
                 _lib.call("b200_hybrid_wgrad_dense", dev, T.data_ptr(), gRf.data_ptr(),
                           dV.data_ptr(), m, d, h, cf, 0, ws.data_ptr(), ws.numel())
             _LAST_TRANSPOSE_OVERFLOW = torch.zeros((), dtype=torch.int32, device=dev)
-            return dX.reshape(X.shape), dG, dK, dV
-        sc = _csc_scratch(dev, m, h)
-        overflow = torch.empty(1, dtype=torch.int32, device=dev)
-        with _Timer("column_lists"):
-            _lib.call("b200_hybrid_csc_build", dev, P.data_ptr(), sc["count"].data_ptr(),
-                      sc["start"].data_ptr(), sc["cursor"].data_ptr(), sc["row"].data_ptr(),
-                      sc["pos"].data_ptr(), sc["cap"], overflow.data_ptr(), m, h, cf)
-        dK = torch.empty((h, d), dtype=torch.bfloat16, device=dev)
-        dG = torch.empty_like(dK)
-        dV = torch.empty_like(dK)
-        with _Timer("spmm_t_dK_dG"):
-            _lib.call("b200_hybrid_spmm_t", dev, dR.data_ptr(), dU.data_ptr(),
-                      sc["start"].data_ptr(), sc["row"].data_ptr(), sc["pos"].data_ptr(),
-                      sc["cap"], Xf.data_ptr(), dK.data_ptr(), dG.data_ptr(), h, d)
-        with _Timer("spmm_t_dV"):
-            _lib.call("b200_hybrid_spmm_t", dev, T.data_ptr(), None, sc["start"].data_ptr(),
-                      sc["row"].data_ptr(), sc["pos"].data_ptr(), sc["cap"], gRf.data_ptr(),
-                      dV.data_ptr(), None, h, d)
-        _LAST_TRANSPOSE_OVERFLOW = overflow.reshape(())
+        else:
+            sc = _csc_scratch(dev, m, h)
+            overflow = torch.empty(1, dtype=torch.int32, device=dev)
+            with _Timer("column_lists"):
+                _lib.call("b200_hybrid_csc_build", dev, P.data_ptr(), sc["count"].data_ptr(),
+                          sc["start"].data_ptr(), sc["cursor"].data_ptr(), sc["row"].data_ptr(),
+                          sc["pos"].data_ptr(), sc["cap"], overflow.data_ptr(), m, h, cf)
+            with _Timer("spmm_t_dK_dG"):
+                _lib.call("b200_hybrid_spmm_t", dev, dR.data_ptr(), dU.data_ptr(),
+                          sc["start"].data_ptr(), sc["row"].data_ptr(), sc["pos"].data_ptr(),
+                          sc["cap"], Xf.data_ptr(), dK.data_ptr(), dG.data_ptr(), h, d)
+            with _Timer("spmm_t_dV"):
+                _lib.call("b200_hybrid_spmm_t", dev, T.data_ptr(), None, sc["start"].data_ptr(),
+                          sc["row"].data_ptr(), sc["pos"].data_ptr(), sc["cap"], gRf.data_ptr(),
+                          dV.data_ptr(), None, h, d)
+            _LAST_TRANSPOSE_OVERFLOW = overflow.reshape(())
+        if tail is not None:
+            # the flagged rows, dense (gate, up and the pattern recomputed from X)
+            with _Timer("dense_tail_backward"):
+                idx, valid, scatter = tail
+                keep = valid.unsqueeze(1)
+                Xt = Xf[idx] * keep
+                gRt = gRf[idx] * keep
+                Pt = torch.relu(Xt @ G.t())
+                Rt = Xt @ K.t()
+                dTt = gRt @ V.t()
+                if gl1_dev is not None:
+                    dTt = dTt + (gl1_dev * (1.0 / m)).to(torch.bfloat16) * torch.sign(Rt)
+                dTt = dTt * (Pt > 0)
+                dRt = dTt * Pt
+                dUt = dTt * Rt
+                dX.index_copy_(0, scatter, dRt @ K + dUt @ G)
+                dK = (dK.float() + (dRt.t() @ Xt).float()).to(torch.bfloat16)
+                dG = (dG.float() + (dUt.t() @ Xt).float()).to(torch.bfloat16)
+                dV = (dV.float() + ((Rt * Pt).t() @ gRt).float()).to(torch.bfloat16)
+            dX = dX[:m]
     return dX.reshape(X.shape), dG, dK, dV
 
 

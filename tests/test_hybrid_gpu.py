@@ -161,3 +161,82 @@ def test_bad_inputs_raise():
         torch.ops.sparse_ops.ff_forward_gated(x[0], w, w, w)
     with pytest.raises(Exception):
         torch.ops.sparse_ops.ff_forward_gated(x, w, w[:256], w)
+
+
+def _mixed_density_case(b, s, d, h, dense_fraction=0.05):
+    """Tokens at about 3 % gate density, ``dense_fraction`` of them at 20-40 % (their feature
+    0, which carries the gate shift, is scaled down): the prefill mix of the kernel-3 route."""
+    ffn = synthetic.make_ffn(d, h, seed=41, density=0.03, skew_sigma=0.5)
+    x = synthetic.make_tokens(b * s, d, seed=42)
+    gen = torch.Generator().manual_seed(43)
+    dense_rows = torch.rand(b * s, generator=gen) < dense_fraction
+    dense_rows[0] = True
+    scale = 0.12 + 0.28 * torch.rand(b * s, generator=gen)
+    x[dense_rows, 0] = (x[dense_rows, 0].float() * scale[dense_rows]).to(x.dtype)
+    gout = synthetic.make_tokens(b * s, d, seed=44, fold_bias=False).reshape(b, s, d)
+    return ffn, x.reshape(b, s, d), gout, dense_rows
+
+
+@pytest.mark.parametrize("adaptive", [False, True])
+def test_dense_tail_keeps_overflowed_rows_exact(wgrad_mode, adaptive):
+    """5 % of the tokens fire 20-40 % of the neurons: far more than a slab holds.  With the
+    dense tail (discard_overflow = 0, the default) nothing is dropped and outputs, l0, l1 and
+    all four gradients meet the usual tolerances against fp32 autograd
+    (custom_op.cpp:79-116, hybrid_sp.cu:811-952, :1358-1383)."""
+    b, s, d, h = 2, 320, 512, 2048
+    ffn, x, gout, dense_rows = _mixed_density_case(b, s, d, h)
+    coeff = 0.05
+    ref = dense_reference(x, ffn.gate, ffn.up, ffn.down, gout, coeff)
+    sparse_ops.set_tail_rows_adaptive(adaptive)
+    try:
+        for step in range(3 if adaptive else 1):  # adaptive: later calls size the tail from earlier ones
+            X = x.to(DEV).requires_grad_(True)
+            G, K, V = (t.to(DEV).requires_grad_(True) for t in (ffn.gate, ffn.up, ffn.down))
+            if step:
+                torch.cuda.synchronize()  # let the count read-back of the previous call land
+            out, l0, l1, P, R, T = torch.ops.sparse_ops.ff_forward_gated(X, G, K, V)
+            ((out.float() * gout.to(DEV).float()).sum() + coeff * l1).backward()
+            torch.cuda.synchronize()
+            with torch.no_grad():
+                direct = sparse_ops.ff_forward_gated(X.detach(), G.detach(), K.detach(), V.detach())
+            assert int(direct[3].overflow_count_tensor().item()) == 0
+            flagged = (P.view(b * s, h // 256, -1)[:, :, 0] < 0).any(dim=1).cpu()
+            assert flagged.sum() >= dense_rows.sum() * 0.9 and flagged.sum() < 0.2 * b * s
+            assert rel_l2(out, ref[0]) < REL_OUT
+            assert abs(l0.item() - ref[1].item()) <= 0.02 * ref[1].item() + 0.05
+            assert abs(l1.item() - ref[2].item()) <= 1e-2 * abs(ref[2].item())
+            for got, want, name in ((X.grad, ref[3], "dX"), (G.grad, ref[4], "dG"),
+                                    (K.grad, ref[5], "dK"), (V.grad, ref[6], "dV")):
+                assert rel_l2(got, want) < REL_GRAD, (name, step, rel_l2(got, want))
+    finally:
+        sparse_ops.set_tail_rows_adaptive(False)
+
+
+def test_discard_mode_drops_and_counts_what_the_tail_would_keep():
+    """set_discard_overflow(1) (custom_op.cpp:92-97): no tail, entries past a tile's capacity
+    are lost and counted; set_tail_rows_regular(0) behaves the same; a capacity below the
+    number of overflowed rows keeps the first rows exact and counts the rest."""
+    b, s, d, h = 2, 320, 512, 2048
+    ffn, x, gout, dense_rows = _mixed_density_case(b, s, d, h)
+    ref_out = dense_reference(x, ffn.gate, ffn.up, ffn.down, gout, 0.0)[0]
+    X, G, K, V = (t.to(DEV) for t in (x, ffn.gate, ffn.up, ffn.down))
+    cfg = torch.ops.sparse_ops_config
+    try:
+        out, *_, P, _, _ = sparse_ops.ff_forward_gated(X, G, K, V)
+        assert int(P.overflow_count_tensor().item()) == 0 and rel_l2(out, ref_out) < REL_OUT
+        cfg.set_discard_overflow(1)
+        out, *_, P, _, _ = sparse_ops.ff_forward_gated(X, G, K, V)
+        dropped_all = int(P.overflow_count_tensor().item())
+        assert dropped_all > 0 and rel_l2(out, ref_out) > 5 * REL_OUT
+        assert not bool((P.slab.view(b * s, h // 256, -1)[:, :, 0] < 0).any())
+        cfg.set_discard_overflow(0)
+        cfg.set_tail_rows_regular(0)
+        out, *_, P, _, _ = sparse_ops.ff_forward_gated(X, G, K, V)
+        assert int(P.overflow_count_tensor().item()) == dropped_all
+        cfg.set_tail_rows_regular(8)  # fewer rows than overflowed
+        out, *_, P, _, _ = sparse_ops.ff_forward_gated(X, G, K, V)
+        some = int(P.overflow_count_tensor().item())
+        assert 0 < some < dropped_all
+    finally:
+        cfg.set_discard_overflow(0)
+        cfg.set_tail_rows_regular(2048)

@@ -1,13 +1,15 @@
-"""Sparsity bookkeeping on CPU: the tracker mirror against vectors generated from the
-reference's SparsityTracker (custom_models/sparse_models.py:95-256; generator:
-tests/golden/make_golden.py --only-tracker), and the oracle's slab-level activity count
-against the dense definition."""
+"""Sparsity bookkeeping on CPU: the oracle's l0 / l1 / dead-neuron update (and the staged
+reference SparsityTracker itself) against vectors generated from the reference's tracker
+(custom_models/sparse_models.py:95-256; generator: tests/golden/make_golden.py
+--only-tracker), the patch helpers, and the oracle's slab-level activity count against the
+dense definition."""
 import contextlib
 import importlib.util
 import io
 import json
 import os
 import sys
+import types
 from pathlib import Path
 
 import numpy as np
@@ -28,55 +30,30 @@ def _generator():
     return gen
 
 
-def test_tracker_reproduces_the_reference_vectors(monkeypatch):
+def test_oracle_and_reference_tracker_reproduce_the_golden_vectors(monkeypatch, ref_models):
     monkeypatch.delenv("WORLD_SIZE", raising=False)
     gen = _generator()
     golden = json.loads((GOLDEN / "sparsity_tracker.json").read_text())
-    tr = tracking.SparsityTracker(**gen.TRACKER_ARGS)
+    with contextlib.redirect_stdout(io.StringIO()):
+        tr = ref_models.SparsityTracker(**gen.TRACKER_ARGS)
     shadow = None
     for layers, want in zip(gen.tracker_inputs(), golden, strict=True):
         if shadow is None:
             shadow = [torch.zeros(h.shape[-1], dtype=torch.int64) for h in layers]
         tr.start_forward_pass()
+        l1s = []
         for i, h in enumerate(layers):
             tr.record_activations(layer_idx=i, absolute_activations=h)
             _, shadow[i] = fo.last_activated_update(h, shadow[i], tr._microbatch_tokens)
+            l1s.append(fo.l0_l1(h)[1])
         l1, stats = tr.finalize_forward_pass()
         assert float(l1) == pytest.approx(want["l1"], rel=1e-6)
+        assert float(torch.stack(l1s).mean()) == pytest.approx(want["l1"], rel=1e-6)
         assert {k: float(v) for k, v in stats.items()} == pytest.approx(want["stats"], rel=1e-6)
         for i in range(len(layers)):
             assert tr._last_activated[i].tolist() == want["last_activated"][i]
             assert shadow[i].tolist() == want["last_activated"][i]  # the oracle agrees too
         assert [int(a.sum()) for a in tr.get_alive_neurons()] == want["alive"]
-
-
-def test_tracker_gating_rules():
-    tr = tracking.SparsityTracker(4, 8, 1, total_devices=2)
-    assert (tr._batch_tokens, tr._microbatch_tokens, tr._tokens_until_dead) == (16, 8, 16)
-    with pytest.raises(ValueError, match="finalize_forward_pass"):
-        tr.get_alive_neurons()
-    h = torch.rand(1, 8, 256)
-    tr.record_activations(0, h)                 # inactive, grad enabled: ignored
-    assert tr._l1_per_layer == [] and 0 not in tr._last_activated
-    with torch.no_grad():
-        tr.record_activations(0, h)             # inactive, no grad: L1 only
-    assert len(tr._l1_per_layer) == 1 and tr._l0_per_layer == []
-    assert int(tr._last_activated[0].sum()) == 0
-    l1, stats = tr.finalize_forward_pass()
-    assert stats == {} and float(l1) == pytest.approx(float(h.sum(-1).mean()))
-    assert tracking.SparsityTracker(4, 8, 1).finalize_forward_pass() == (0.0, {})
-    null = tracking.NullTracker(4, 8)
-    null.record_pattern(0, None, None, None)
-    assert null.finalize_forward_pass()[1] == {}
-
-
-def test_record_l0_l1_leaves_counters_stale_like_the_reference():
-    tr = tracking.SparsityTracker(4, 8, 1)
-    tr.start_forward_pass()
-    tr.record_l0_l1(0, torch.tensor(3.0), torch.tensor(0.5), width=256)
-    assert tr._last_activated[0].shape == (256,) and int(tr._last_activated[0].sum()) == 0
-    _, stats = tr.finalize_forward_pass()
-    assert float(stats["activation_l0/mean"]) == 3.0
 
 
 class _FakeSparseMLP(torch.nn.Module):
@@ -172,7 +149,10 @@ def test_record_pattern_function_falls_back_for_trackers_without_counters():
 
     tracking.record_pattern(Plain(), 3, 1.0, 2.0, P=None, T=None, width=256)
     assert calls == [{"layer_idx": 3, "l0": 1.0, "l1": 2.0, "width": 256}]
-    tr = tracking.SparsityTracker(4, 8, 1)                   # inactive + grad enabled: ignored
+    # a tracker with the reference's fields, inactive while grad is enabled: ignored
+    tr = types.SimpleNamespace(active=False, _l1_per_layer=[], _l0_per_layer=[],
+                               _last_activated={}, _microbatch_tokens=8,
+                               register_layer=lambda *a, **k: None)
     tracking.record_pattern(tr, 0, None, None, P=torch.zeros(2, 64, dtype=torch.int32))
     assert tr._l1_per_layer == [] and tr._last_activated == {}
 

@@ -60,12 +60,14 @@ def test_activity_matches_the_oracle_on_the_same_slabs(b, s, d, h, density, widt
     assert pat.sum() == stored
 
 
-def test_record_pattern_equals_record_activations_on_the_dense_activation():
+def test_record_pattern_equals_record_activations_on_the_dense_activation(ref_models):
     torch.ops.sparse_ops_config.set_ell_width_regular(128)
     cf = sparse_ops.compression_factor()
     b, s, d, h = 2, 64, 512, 1024
-    fused = tracking.SparsityTracker(8, s, b, tokens_until_dead=2 * b * s)
-    dense = tracking.SparsityTracker(8, s, b, tokens_until_dead=2 * b * s)
+    make = lambda: ref_models.SparsityTracker(train_batch_size=8, max_seq_len=s,  # noqa: E731
+                                              per_device_train_batch_size=b,
+                                              tokens_until_dead=2 * b * s)
+    fused, dense = make(), make()
     for step in range(4):
         # from step 1 on, neurons 0..199 stop firing and die two steps later
         _, l0, l1, P, _, T = forward(b, s, d, h, 0.04, 50 + step,
@@ -74,7 +76,7 @@ def test_record_pattern_equals_record_activations_on_the_dense_activation():
             T.cpu().numpy().view(np.uint32), h, cf))).reshape(b, s, h)
         fused.start_forward_pass()
         dense.start_forward_pass()
-        fused.record_pattern(0, l0, l1, P, T)
+        tracking.record_pattern(fused, 0, l0, l1, P, T)
         dense.record_activations(0, h_abs.to(DEV))
         l1_f, stats_f = fused.finalize_forward_pass()
         l1_d, stats_d = dense.finalize_forward_pass()
@@ -86,7 +88,7 @@ def test_record_pattern_equals_record_activations_on_the_dense_activation():
     assert int(fused.get_alive_neurons()[0].sum()) > 0
 
 
-def test_patched_module_keeps_counters_live_through_forward_and_backward():
+def test_patched_module_keeps_counters_live_through_forward_and_backward(ref_models):
     """A module with the reference SparseMLP's attributes (kernel-layout weights, tracker,
     layer_idx; custom_models/sparse_models.py:262-395), patched: the fused training branch
     runs under autograd and ages / revives the counters."""
@@ -109,7 +111,8 @@ def test_patched_module_keeps_counters_live_through_forward_and_backward():
         def forward(self, x):
             raise AssertionError("the fused branch must not reach the module's own forward")
 
-    tr = tracking.SparsityTracker(b, s, b, tokens_until_dead=b * s)
+    tr = ref_models.SparsityTracker(train_batch_size=b, max_seq_len=s,
+                                    per_device_train_batch_size=b, tokens_until_dead=b * s)
     mlp = Mlp(tr).to(DEV).to(torch.bfloat16)
     tracking.enable_live_dead_neuron_tracking(mlp)
     for step in range(2):

@@ -391,3 +391,68 @@ def test_tcgen05_pack_kernel_gaussian_with_bias_at_prefill_size():
     sel = (dense > 0) & (ref > 1e-3)
     assert ((dense - ref).abs()[sel] <= 0.01 * ref[sel] + 1e-3).all()
     assert sel.float().mean() > 0.02
+
+
+def test_config1_golden_case_through_the_fused_mlp(golden_dir):
+    """The single-layer configuration (256 tokens, d_model 1024, d_ff 4096, constant gate shift
+    for about 2 % density) whose outputs the reference's SparseMLP produced
+    (tests/golden/config1_gated.npz): b200_twell_gated_mlp at cf = 2, the width the fixture's
+    counts were taken at."""
+    import hashlib
+    g = np.load(golden_dir / "config1_gated.npz")
+    m, d, h = int(g["m"]), int(g["d"]), int(g["h"])
+    gen = torch.Generator().manual_seed(int(g["seed"]))
+    x = torch.randn(m, d, generator=gen)
+    gate = (torch.randn(h, d, generator=gen) * 0.02).to(torch.bfloat16)
+    up = (torch.randn(h, d, generator=gen) * 0.02).to(torch.bfloat16)
+    down = (torch.randn(h, d, generator=gen) * 0.02).to(torch.bfloat16)
+    x = x.to(torch.bfloat16)
+    sha = hashlib.sha256()
+    for t in (x, gate, up, down):
+        sha.update(t.view(torch.int16).numpy().tobytes())
+    assert sha.hexdigest() == str(g["input_sha"])
+    bias = torch.full((h,), float(g["shift"]))
+    mod = twell.TwELLGatedMLP(9100, gate, up, down, compression_factor=2,
+                              flex_kernels=True).to(DEV)
+    y = mod(x.to(DEV))  # creates the cached layer
+    twell.set_d2t_layer_bias(9100, bias.to(DEV))
+    y = mod(x.to(DEV))
+    packed = twell.allocate_packed_output(m, h, device=DEV, compression_factor=2)
+    twell.run_d2t_layer(9100, x.to(DEV), packed)
+    torch.cuda.synchronize()
+    counts = tf.slab_counts(to_np_u32(packed), 2)
+    want = g["counts"].astype(np.int64)
+    # counts: bit-exact outside the ambiguity band of the fp32 accumulation order
+    amb, _ = fo.ambiguity_mask(x, gate, bias, rel=4e-6)
+    slack = amb.numpy().reshape(m, h // 256, 256).sum(-1)
+    assert (np.abs(counts - want) <= slack).all()
+    assert (counts != want).mean() < 1e-3
+    # outputs: the reference's fp32 torch rows, mixed-mode tolerance
+    got = y.float().cpu()
+    _, rel = fo.max_abs_and_rel_l2(got[:32], torch.from_numpy(g["y_rows"]))
+    assert rel < REL_L2_MIXED, rel
+    assert abs(float(got.double().norm()) - float(g["y_norm"])) < 2e-2 * float(g["y_norm"])
+    mod.destroy()
+
+
+@pytest.mark.parametrize("m", [16, 1024])
+def test_kernel_sweep_shape_against_the_oracle(m):
+    """d_model 4096, d_ff 16384 (the kernel-sweep shape): slab counts against the fp64 oracle
+    outside the ambiguity band, output rows against the oracle fed the kernel's own slab."""
+    d, h = 4096, 16384
+    ffn = synthetic.make_ffn(d, h, seed=31, density=0.02, skew_sigma=1.0)
+    x = synthetic.make_tokens(m, d, seed=32)
+    xg, g, u, dn = x.to(DEV), ffn.gate.to(DEV), ffn.up.to(DEV), ffn.down.to(DEV)
+    packed = gpu_pack(xg, g, 8)
+    got = twell.matmul_gated_t2d(xg, packed, u, dn)
+    torch.cuda.synchronize()
+    slab = to_np_u32(packed)
+    rows = min(24, m)  # the fp64 pre-activations of a prefix of rows
+    amb, z64 = fo.ambiguity_mask(x[:rows], ffn.gate, rel=4e-6)
+    c64 = (z64 > 0).numpy().reshape(rows, h // 256, 256).sum(-1)
+    slack = amb.numpy().reshape(rows, h // 256, 256).sum(-1)
+    assert (np.abs(tf.slab_counts(slab[:rows], 8) - c64) <= slack).all()
+    mo = 6
+    want = fo.gated_t2d(x[:mo], slab[:mo], ffn.up, ffn.down)
+    _, rel = fo.max_abs_and_rel_l2(got[:mo].float().cpu(), want)
+    assert rel < REL_L2_SAME_SLAB, rel

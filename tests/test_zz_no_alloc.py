@@ -6,9 +6,11 @@ framework): its scratch lives in a fixed array inside the library.  This file is
 that pytest collects it last; it must pass alone in a fresh process and after every other
 test, because the built-in array is shared by all calls of the process.
 """
+import numpy as np
 import pytest
 import torch
 
+from oracle import ffn_oracle as fo
 from sparser_faster_llms_b200 import _lib, synthetic, twell
 
 pytestmark = pytest.mark.gpu
@@ -49,6 +51,12 @@ def test_noalloc_matches_existing_entry_point_twice_in_a_row(m, hp):
         rel = ((y - ref).norm() / ref.norm()).item()
         assert rel < REL_L2_SAME_SLAB, rel
     assert torch.equal(outs[0], outs[1])
+    # and against the CPU oracle fed the same slab (a prefix of rows: the loop oracle is slow)
+    mo = min(m, 4)
+    slab = packed[:mo].cpu().view(torch.int32).numpy().view(np.uint32)
+    want = fo.gated_t2d(x[:mo].cpu(), slab, ffn.up.cpu(), ffn.down.cpu(), highest_precision=hp)
+    _, rel = fo.max_abs_and_rel_l2(outs[0][:mo].cpu(), want)
+    assert rel < REL_L2_SAME_SLAB, rel
 
 
 def test_noalloc_rejects_sizes_beyond_the_builtin_scratch():
