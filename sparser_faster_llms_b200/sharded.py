@@ -165,7 +165,13 @@ class ShardedTwELLGatedMLP(nn.Module):
 
     def forward(self, A: torch.Tensor) -> torch.Tensor:
         if self._fused_ready(A):
-            return self.local(A)  # the contraction's epilogue has already summed the shards
+            try:
+                return self.local(A)  # the contraction's epilogue has already summed the shards
+            except ValueError as exc:
+                # the library refuses a fused call whose grid is not resident at once (the same
+                # decision on every rank: identical GPUs); such calls take the unfused route
+                if "fused all-reduce" not in str(exc):
+                    raise
         if self.fused_allreduce is not None:
             from . import twell
             entry = twell._D2T_LAYERS.get(int(getattr(self.local, "layer_number", -1)))

@@ -51,6 +51,10 @@ def main() -> None:
     ap.add_argument("--hbm-gbs", type=float, default=6552.6)
     ap.add_argument("--bf16-tflops", type=float, default=1620.9)
     args = ap.parse_args()
+    import os
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        return sharded_sweep(args)
     dev = torch.device("cuda", torch.cuda.current_device())
     d, h = args.d_model, args.d_ff
     for skew in [float(s) for s in args.skews.split(",")]:
@@ -103,6 +107,72 @@ def main() -> None:
                 print(json.dumps(rec), flush=True)
             for mod in (sparse, routed, dense):
                 mod.destroy()
+
+
+def sharded_sweep(args) -> None:
+    """Under torchrun: the TwELL path with d_ff sharded over the ranks (pack + contraction on
+    each shard, shard sum inside the contraction kernel up to 256 tokens, through NCCL beyond)
+    against the unsharded cuBLAS formula on rank 0's GPU.  Time = max over ranks."""
+    import os
+    import sys
+
+    import torch.distributed as dist
+
+    from . import peer_allreduce, sharded
+    world, rank = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"])
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    d, h = args.d_model, args.d_ff
+    tokens = [int(s) for s in args.tokens.split(",")]
+    small = [m for m in tokens if m <= 256]
+    far = par = None
+    if small:
+        par = peer_allreduce.PeerAllReduce(max(small) * d * 2, device=dev)
+        far = peer_allreduce.FusedShardAllReduce(max(small), d, device=dev)
+    for skew in [float(s) for s in args.skews.split(",")]:
+        for rho in [float(s) for s in args.densities.split(",")]:
+            ffn = synthetic.make_ffn(d, h, seed=11, density=rho, skew_sigma=skew)
+            g, u, dn = ffn.gate.to(dev), ffn.up.to(dev), ffn.down.to(dev)
+            mod = sharded.ShardedTwELLGatedMLP(5100, g, u, dn, rank=rank, world_size=world,
+                                               peer_allreduce=par, fused_allreduce=far)
+            for m in tokens:
+                x = synthetic.make_tokens(m, d, seed=12).to(dev)
+                reps = 20 if m <= 1024 else 5
+                mod(x)
+                torch.cuda.synchronize(dev)
+                dist.barrier()
+                t = torch.tensor([_time(lambda: mod(x), reps)], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                rec = {"tokens": m, "density": rho, "skew": skew, "d_model": d, "d_ff": h,
+                       "n_gpus": world, "sharded_sparse_us": float(t.item())}
+                if rank == 0:
+                    def cublas():
+                        return (torch.relu(x @ g.T) * (x @ u.T)) @ dn
+                    ref = cublas().float()
+                    rec["cublas_unsharded_us"] = _time(cublas, reps)
+                    rec["rel_l2_vs_cublas"] = float((mod_out(mod, x) - ref).norm() / ref.norm())
+                else:
+                    mod_out(mod, x)
+                if rank == 0:
+                    print(json.dumps(rec), flush=True)
+                torch.cuda.synchronize(dev)
+                dist.barrier()
+            mod.destroy()
+    if par is not None:
+        par.fused = far
+        par.close()
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
+
+
+def mod_out(mod, x):
+    """One more (collective) forward on every rank, as fp32."""
+    y = mod(x).float()
+    torch.cuda.synchronize()
+    return y
 
 
 if __name__ == "__main__":

@@ -52,6 +52,10 @@ def main() -> None:
     ap.add_argument("--l1-coeff", type=float, default=3e-4)
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--adaptive-tail", type=int, default=1,
+                    help="1: size the dense tail from the overflow rows seen on earlier calls "
+                         "(sparse_ops.set_tail_rows_adaptive); 0: always tail_rows_regular rows")
+    ap.add_argument("--tail-rows", type=int, default=2048)
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -61,6 +65,8 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     sparse_ops.register_ops()
+    sparse_ops.set_tail_rows_adaptive(bool(args.adaptive_tail))
+    torch.ops.sparse_ops_config.set_tail_rows_regular(args.tail_rows)
     b, s, d, h = args.batch, args.seq, args.d_model, args.d_ff
     ffn = synthetic.make_ffn(d, h, seed=21, density=args.density, skew_sigma=1.0)
     x = synthetic.make_tokens(b * s, d, seed=22).view(b, s, d).to(dev).requires_grad_(True)
@@ -118,7 +124,8 @@ def main() -> None:
         tokens = b * s
         print(json.dumps({
             "n_gpus": world, "tokens": tokens, "d_model": d, "d_ff": h, "l0_per_token": float(l0),
-            "dtype": "bf16", "data": "synthetic", **res,
+            "dtype": "bf16", "data": "synthetic", "adaptive_tail": bool(args.adaptive_tail),
+            "tail_rows": args.tail_rows, **res,
             "sparse_tokens_per_s": tokens / (res["sparse"]["forward_backward_ms"] * 1e-3),
             "dense_tokens_per_s": tokens / (res["dense"]["forward_backward_ms"] * 1e-3)}), flush=True)
     if world > 1:
