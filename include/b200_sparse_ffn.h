@@ -128,9 +128,13 @@ int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias
 /*
  * The fused gated MLP as ONE kernel for decode-sized calls (1 <= M <= 32): a thread-block
  * cluster per 256-neuron tile computes its slice of the gate, writes the slab words (same
- * bytes as b200_twell_pack) and at once contracts its own active neurons - every active up /
- * down row is fetched once per call, staged in shared memory by cp.async.bulk, however many
- * tokens fire it - and the tiles' partial sums meet in the workspace.  Replaces the
+ * bytes as b200_twell_pack) and at once contracts its own active neurons, and the tiles'
+ * partial sums meet in the workspace.  Two forms: up to 16 tokens at D = 2048 or 4096 the
+ * mma.sync pack kernel with the contraction appended (each finalising CTA gathers the rows of
+ * its token's active neurons with 128-bit loads; the last tile of a token to arrive sums the
+ * tiles' rows, so no CTA waits for another and any H is served); otherwise the tcgen05 form
+ * (every active up / down row is fetched once per call, staged in shared memory by
+ * cp.async.bulk, however many tokens fire it; its CTAs meet at a bounded barrier).  Replaces the
  * reference's two launches per layer (custom_models/twell_modules/mlp_twell.cu:126-152:
  * matmul_d2t.cu:287-709 followed by matmul_gated_t2d.cu:17-169).
  *   workspace: at least b200_twell_decode_workspace_bytes(M, D, H) bytes (0 = this shape is
@@ -140,14 +144,16 @@ int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias
  *   prefetch / prefetch_bytes: optional range of this GPU's memory (16-byte aligned) that the
  *     kernel asks L2 to prefetch while it runs, e.g. the next layer's gate matrix, which does
  *     not depend on this layer's result; NULL / 0 = none.
- * The CTAs of the grid wait for one another (bounded): the call needs the GPU to itself while
- * it runs; the host checks with cudaOccupancyMaxActiveClusters that the grid is resident at
- * once.  Returns B200_EUNSUPPORTED when the shape, the workspace or the residency check rules
- * the kernel out.  b200_twell_gated_mlp / b200_twell_mlp take this path by themselves only
- * when the environment variable B200_DECODE_FUSED=1 is set and their workspace argument is
- * large enough: measured on B200 the two-kernel form is the faster one (17.0 / 20.2 / 25.3 us
- * per layer at 1 / 8 / 32 tokens against 23.9 / 30.3 / 44.4 us at D = 2048, H = 8192), because
- * each of this kernel's serial phases costs 1.5-4 us of latency with one resident CTA per SM.
+ * In the tcgen05 form the CTAs of the grid wait for one another (bounded): the call needs the
+ * GPU to itself while it runs; the host checks with cudaOccupancyMaxActiveClusters that the
+ * grid is resident at once.  Returns B200_EUNSUPPORTED when the shape, the workspace or the
+ * residency check rules the kernel out.  b200_twell_gated_mlp / b200_twell_mlp take this path
+ * by themselves only when the environment variable B200_DECODE_FUSED is 1 (every call a form
+ * serves) or 2 (the mma.sync form only) and their workspace argument is large enough:
+ * measured on B200 at D = 2048, H = 8192 the two-kernel form is the faster one - 16.7 / 20.2 /
+ * 23.9 / 24.8 us per layer at 1 / 8 / 16 / 32 tokens against 20.2 / 23.1 / 33.6 us (mma.sync
+ * form, 1 / 8 / 16 tokens) and 44.1 us (tcgen05 form, 32 tokens) - because each serial phase
+ * of a one-kernel form costs 0.3-4 us of latency that the launch it saves does not pay for.
  */
 size_t b200_twell_decode_workspace_bytes(int64_t M, int64_t D, int64_t H);
 
@@ -389,6 +395,17 @@ int b200_twell_gated_mlp_allreduce(const void* x, const void* gate, const float*
 /* 0, or 0x100 + peer rank if a wait for that peer gave up; -1 if unreadable.  Reads and
  * clears the word; synchronises the device. */
 int b200_fused_allreduce_status(void* my_block);
+
+/*
+ * Residual add + RMSNorm of a few token rows in one kernel (the element-wise steps around the
+ * FFN of a decoder layer; no counterpart in the reference, whose models run them as separate
+ * torch modules around the MLP swap point, custom_models/sparse_models.py:552-614):
+ *   x_out[r,:] = x[r,:] + delta[r,:]            (delta may be NULL; x_out may alias x or be NULL)
+ *   h_out[r,:] = x_out[r,:] * rsqrt(mean(x_out[r,:]^2) + eps) * weight[:]
+ * bf16 in and out, fp32 inside; D % 8 == 0, D <= 8192; h_out must not alias the others.
+ */
+int b200_residual_rmsnorm(const void* x, const void* delta, const void* weight, float eps,
+                          void* x_out, void* h_out, int64_t M, int64_t D, void* stream);
 
 /*
  * Gated contraction for hosts that may not allocate device memory (no counterpart

@@ -103,6 +103,9 @@ _PROTOTYPES = {
                                             c_void_p]),
     "b200_twell_decode_status": (c_int, []),
     "b200_l2_prefetch": (c_int, [c_void_p, c_int64, c_void_p]),
+    # x, delta, weight, eps, x_out, h_out, M, D, stream
+    "b200_residual_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                      c_int64, c_int64, c_void_p]),
     "b200_twell_mlp": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
 }

@@ -46,26 +46,39 @@ int twell_decode_launch(bool gated, bool hp, const void* x, const void* gate, co
                         int64_t D, int64_t H, int cf, void* workspace, size_t workspace_bytes,
                         const void* pf_ptr, int64_t pf_bytes, cudaStream_t stream,
                         bool probe_only);
+bool twell_decode_small_serves(int64_t M, int64_t D, int64_t H);
+size_t twell_decode_small_workspace_bytes(int64_t M, int64_t D, int64_t H);
+int twell_decode_small_launch(bool gated, bool hp, const void* x, const void* w,
+                              const float* bias, const void* up, const void* down, void* packed,
+                              void* out, int64_t M, int64_t D, int64_t H, int cf, void* workspace,
+                              size_t workspace_bytes, cudaStream_t stream);
 int l2_prefetch_launch(const void* p, int64_t bytes, cudaStream_t stream);
 int twell_decode_status();
 #ifdef B200_TRACE
 void twell_decode_trace(unsigned long long* out16);
 #endif
 
-// Whether b200_twell_gated_mlp / b200_twell_mlp hand decode-sized calls to the one-kernel
-// form when the caller's workspace is large enough.  Off unless B200_DECODE_FUSED=1: measured
-// on B200 (D 2048, H 8192, 28 layers under graph replay) the one-kernel form takes 23.9 / 30.3 /
-// 44.4 us per layer at 1 / 8 / 32 tokens against 17.0 / 20.2 / 25.3 us for pack + contraction -
-// its six phases (split-k exchange, finalise, lists, row staging, cross-tile barrier, sum) each
-// cost 1.5-4 us of latency on one resident CTA per SM, more than the launch and slab round
-// trip they save.
-bool decode_fused_enabled() {
-  static int on = -1;
-  if (on < 0) {
+// Which calls b200_twell_gated_mlp / b200_twell_mlp hand to a one-kernel decode form when the
+// caller's workspace is large enough (environment variable B200_DECODE_FUSED):
+//   0  none (always pack + contraction),
+//   2  the mma.sync form for up to 16 tokens only,
+//   1  every call a one-kernel form serves (the tcgen05 form for 17..32 tokens as well).
+// Measured on B200 (D 2048, H 8192, 28 layers under graph replay) the tcgen05 form takes
+// 44 us per layer at 32 tokens against 25 us for pack + contraction - its serial phases
+// (split-k exchange, finalise, lists, row staging, cross-tile barrier, sum) each cost 0.3-4 us of
+// latency on one resident CTA per SM, more than the launch and slab round trip they save - so
+// it is never the default.
+#ifndef B200_DECODE_FUSED_DEFAULT
+#define B200_DECODE_FUSED_DEFAULT 0
+#endif
+int decode_fused_mode() {
+  static int mode = -1;
+  if (mode < 0) {
     const char* e = getenv("B200_DECODE_FUSED");
-    on = (e != nullptr && atoi(e) == 1) ? 1 : 0;
+    const int v = e != nullptr ? atoi(e) : B200_DECODE_FUSED_DEFAULT;
+    mode = (v == 1 || v == 2) ? v : 0;
   }
-  return on != 0;
+  return mode;
 }
 
 int pdl_mask() {
@@ -218,8 +231,36 @@ int b200_hybrid_spmm(const void* vals_slab, const void* b_rows, void* out, int64
 
 size_t b200_twell_decode_workspace_bytes(int64_t M, int64_t D, int64_t H) {
   if (M < 0 || D <= 0 || H <= 0 || D % 256 || H % 256) return 0;
+  if (twell_decode_small_serves(M, D, H)) return twell_decode_small_workspace_bytes(M, D, H);
   return twell_decode_workspace_bytes(M, D, H);
 }
+
+namespace {
+// The one-kernel decode forms: the mma.sync form for up to 16 tokens (d_model 2048 / 4096), the
+// tcgen05 form otherwise.  A prefetch range is only taken by the tcgen05 form.
+bool decode_wanted(int64_t M, int64_t D, int64_t H, const void* workspace,
+                   size_t workspace_bytes) {
+  const int mode = decode_fused_mode();
+  if (mode == 0 || workspace == nullptr || M < 1 || M > 32) return false;
+  if (D < 256 || D % 256 || H < 256 || H % 256) return false;
+  const bool small = twell_decode_small_serves(M, D, H);
+  if (mode == 2 && !small) return false;
+  const size_t need = small ? twell_decode_small_workspace_bytes(M, D, H)
+                            : twell_decode_workspace_bytes(M, D, H);
+  return need > 0 && workspace_bytes >= need;
+}
+
+int decode_dispatch(bool gated, bool hp, const void* x, const void* gate, const float* bias,
+                    const void* up, const void* down, void* packed, void* out, int64_t M,
+                    int64_t D, int64_t H, int cf, void* workspace, size_t workspace_bytes,
+                    const void* pf, int64_t pf_bytes, cudaStream_t stream) {
+  if (twell_decode_small_serves(M, D, H))
+    return twell_decode_small_launch(gated, hp, x, gate, bias, up, down, packed, out, M, D, H, cf,
+                                     workspace, workspace_bytes, stream);
+  return twell_decode_launch(gated, hp, x, gate, bias, up, down, packed, out, M, D, H, cf,
+                             workspace, workspace_bytes, pf, pf_bytes, stream, false);
+}
+}  // namespace
 
 int b200_twell_decode_status(void) { return twell_decode_status(); }
 
@@ -268,25 +309,22 @@ int b200_twell_gated_mlp_decode(const void* x, const void* gate, const float* ga
   if (M == 0) return B200_OK;
   if (prefetch != nullptr && (!aligned16(prefetch) || prefetch_bytes < 0))
     return fail(B200_EALIGN, "%s: prefetch range must be 16-byte aligned and non-negative", fn);
-  return twell_decode_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, gate, gate_bias, up,
-                             down, packed, out, M, D, H, cf, workspace, workspace_bytes, prefetch,
-                             prefetch != nullptr ? prefetch_bytes : 0,
-                             static_cast<cudaStream_t>(stream), false);
+  return decode_dispatch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, gate, gate_bias, up,
+                         down, packed, out, M, D, H, cf, workspace, workspace_bytes, prefetch,
+                         prefetch != nullptr ? prefetch_bytes : 0,
+                         static_cast<cudaStream_t>(stream));
 }
 
 int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias, const void* up,
                          const void* down, void* packed, void* out, int64_t M, int64_t D,
                          int64_t H, int cf, uint32_t flags, void* workspace,
                          size_t workspace_bytes, void* stream) {
-  if (M >= 1 && M <= 32 && workspace != nullptr && decode_fused_enabled() &&
-      workspace_bytes >= twell_decode_workspace_bytes(M, D, H) &&
-      twell_decode_workspace_bytes(M, D, H) > 0) {
+  if (decode_wanted(M, D, H, workspace, workspace_bytes)) {
     B200_TRY(check_decode_args("b200_twell_gated_mlp", x, gate, gate_bias, up, down, packed, out,
                                M, D, H, cf, flags, workspace, true));
-    const int rc = twell_decode_launch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, gate,
-                                       gate_bias, up, down, packed, out, M, D, H, cf, workspace,
-                                       workspace_bytes, nullptr, 0,
-                                       static_cast<cudaStream_t>(stream), false);
+    const int rc = decode_dispatch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, gate,
+                                   gate_bias, up, down, packed, out, M, D, H, cf, workspace,
+                                   workspace_bytes, nullptr, 0, static_cast<cudaStream_t>(stream));
     if (rc != B200_EUNSUPPORTED) return rc;  // served (or failed for good)
   }
   B200_TRY(b200_twell_pack(x, gate, gate_bias, packed, M, D, H, cf, stream));
@@ -361,15 +399,13 @@ int b200_fused_allreduce_status(void* my_block) {
 int b200_twell_mlp(const void* x, const void* up, const void* down, void* packed, void* out,
                    int64_t M, int64_t D, int64_t H, int cf, int num_splits, void* workspace,
                    size_t workspace_bytes, void* stream) {
-  if (M >= 1 && M <= 32 && workspace != nullptr && decode_fused_enabled() &&
-      (num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8) &&
-      workspace_bytes >= twell_decode_workspace_bytes(M, D, H) &&
-      twell_decode_workspace_bytes(M, D, H) > 0) {
+  if ((num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8) &&
+      decode_wanted(M, D, H, workspace, workspace_bytes)) {
     B200_TRY(check_decode_args("b200_twell_mlp", x, up, nullptr, nullptr, down, packed, out, M, D,
                                H, cf, 0, workspace, false));
-    const int rc = twell_decode_launch(false, false, x, up, nullptr, nullptr, down, packed, out, M,
-                                       D, H, cf, workspace, workspace_bytes, nullptr, 0,
-                                       static_cast<cudaStream_t>(stream), false);
+    const int rc = decode_dispatch(false, false, x, up, nullptr, nullptr, down, packed, out, M, D,
+                                   H, cf, workspace, workspace_bytes, nullptr, 0,
+                                   static_cast<cudaStream_t>(stream));
     if (rc != B200_EUNSUPPORTED) return rc;
   }
   B200_TRY(b200_twell_pack(x, up, nullptr, packed, M, D, H, cf, stream));

@@ -7,7 +7,11 @@ ReLU, untied LM head) whose FFN is either the TwELL module of this package or th
 bf16 formula through cuBLAS - the same weights, the same function
 (``SparseMLP._forward_mlp_inference_logic``, custom_models/sparse_models.py:343-351, with the
 gate shift of :mod:`synthetic` as an explicit gate bias).  Attention, norms and the LM head
-are plain torch (cuBLAS / SDPA): they are outside the sparse-FFN path and identical in both
+are library code (cuBLAS, torch's fused RMSNorm, and for the decode step flash-attn's
+``flash_attn_with_kvcache`` - rotary embedding, cache append and attention in one kernel -
+where it runs on the device; torch SDPA otherwise), and in the decode step every "residual
+add, then RMSNorm" pair around the FFN is one launch of this package's
+``b200_residual_rmsnorm``: they are outside the sparse-FFN path and identical in both
 variants.  One decode step (all layers, greedy sampling, KV-cache update, position
 increment) is captured in a CUDA graph and replayed; nothing returns to the host between
 tokens.
@@ -26,7 +30,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from . import synthetic, twell
+from . import norm, synthetic, twell
 
 
 @dataclass
@@ -67,13 +71,15 @@ class SparseDecoder(nn.Module):
     """``ffn`` = "twell" (this package's sparse path) or "dense" (cuBLAS)."""
 
     def __init__(self, cfg: DecoderConfig, batch: int, *, ffn: str = "twell", seed: int = 0,
-                 device="cuda", shard: dict | None = None):
+                 device="cuda", shard: dict | None = None, attn: str = "auto"):
         """``shard = {"rank", "world", "peer_allreduce", "fused_allreduce"}`` splits the d_ff of
         every TwELL FFN over the ranks of a process group (attention, norms and the LM head stay
         replicated); every rank then holds the same activations and generates the same tokens."""
         super().__init__()
         if ffn not in ("twell", "dense"):
             raise ValueError("ffn must be 'twell' or 'dense'")
+        if attn not in ("auto", "flash", "sdpa"):
+            raise ValueError("attn must be 'auto', 'flash' or 'sdpa'")
         self.cfg, self.batch, self.kind = cfg, int(batch), ffn
         self.shard = shard if (shard and shard.get("world", 1) > 1 and ffn == "twell") else None
         dev = torch.device(device)
@@ -115,13 +121,18 @@ class SparseDecoder(nn.Module):
             else:
                 m = DenseGatedFFN(g, u, dn, b)
             self.ffns.append(m)
-        # static KV cache and rotary tables
-        self.k_cache = torch.zeros(cfg.layers, batch, nh, cfg.max_seq, hd, dtype=bf, device=dev)
+        # static KV cache [layers, B, S, heads, head_dim] and rotary tables
+        self.k_cache = torch.zeros(cfg.layers, batch, cfg.max_seq, nh, hd, dtype=bf, device=dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
         ang = torch.outer(torch.arange(cfg.max_seq, dtype=torch.float32), inv)
         self.cos = torch.cat([ang.cos(), ang.cos()], -1).to(dev)  # [max_seq, hd] fp32
         self.sin = torch.cat([ang.sin(), ang.sin()], -1).to(dev)
+        self.cos_half = ang.cos().to(bf).to(dev)                   # [max_seq, hd / 2], decode kernel
+        self.sin_half = ang.sin().to(bf).to(dev)
+        self.seqlens = torch.zeros(batch, dtype=torch.int32, device=dev)  # tokens in the cache
+        self.attn = self._pick_attention(attn, dev)
+        self.fused_norm = dev.type == "cuda"  # residual add + RMSNorm as one library kernel
         # decode-step state (device resident; the captured graph updates it in place)
         self.ids = torch.zeros(batch, dtype=torch.long, device=dev)
         self.pos = torch.zeros(1, dtype=torch.long, device=dev)
@@ -134,7 +145,29 @@ class SparseDecoder(nn.Module):
         self.dev = dev
 
     # -- building blocks --------------------------------------------------------
-    def _rope(self, t, cos, sin):  # t [B, nh, S, hd]; cos/sin [S, hd]
+    def _pick_attention(self, attn: str, dev: torch.device) -> str:
+        """"flash" when flash-attn's kv-cache kernel runs on this device (probed once with a
+        tiny call), else "sdpa"."""
+        if attn == "sdpa" or dev.type != "cuda":
+            if attn == "flash":
+                raise RuntimeError("attn='flash' needs a CUDA device")
+            return "sdpa"
+        try:
+            from flash_attn import flash_attn_with_kvcache
+            q = torch.zeros(1, 1, 2, self.cfg.head_dim, dtype=torch.bfloat16, device=dev)
+            kc = torch.zeros(1, 16, 2, self.cfg.head_dim, dtype=torch.bfloat16, device=dev)
+            flash_attn_with_kvcache(q, kc, kc.clone(), k=q, v=q,
+                                    rotary_cos=self.cos_half[:16], rotary_sin=self.sin_half[:16],
+                                    cache_seqlens=torch.zeros(1, dtype=torch.int32, device=dev),
+                                    causal=True, rotary_interleaved=False)
+            torch.cuda.synchronize(dev)
+            return "flash"
+        except Exception:
+            if attn == "flash":
+                raise
+            return "sdpa"
+
+    def _rope(self, t, cos, sin):  # t [..., S, heads, hd]; cos/sin [S, 1, hd]
         half = t.shape[-1] // 2
         rot = torch.cat([-t[..., half:], t[..., :half]], -1)
         return (t.float() * cos + rot.float() * sin).to(t.dtype)
@@ -143,22 +176,48 @@ class SparseDecoder(nn.Module):
         b, s, d = x.shape
         return self.ffns[l](x.reshape(b * s, d)).view(b, s, d)
 
+    def _attention(self, l, h, cos, sin, write_pos, mask, causal):
+        """Attention block on the normalised hidden state ``h [B, S, D]`` -> ``[B, S, D]``."""
+        cfg = self.cfg
+        b, s, _ = h.shape
+        nh, hd = cfg.heads, cfg.head_dim
+        qkv = F.linear(h, self.wqkv[l]).view(b, s, 3, nh, hd)
+        if not causal and self.attn == "flash":
+            # decode step: rotary embedding of q and k, cache append at seqlens, attention
+            from flash_attn import flash_attn_with_kvcache
+            a = flash_attn_with_kvcache(
+                qkv[:, :, 0], self.k_cache[l], self.v_cache[l], k=qkv[:, :, 1], v=qkv[:, :, 2],
+                rotary_cos=self.cos_half, rotary_sin=self.sin_half, cache_seqlens=self.seqlens,
+                causal=True, rotary_interleaved=False)
+        else:
+            qk = self._rope(qkv[:, :, :2].transpose(0, 2), cos, sin)  # [2, s, b, nh, hd] rotated
+            q, k, v = qk[0].transpose(0, 1), qk[1].transpose(0, 1), qkv[:, :, 2]  # [b, s, nh, hd]
+            self.k_cache[l].index_copy_(1, write_pos, k)
+            self.v_cache[l].index_copy_(1, write_pos, v)
+            if causal:   # prefill: attend inside the prompt only
+                a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2),
+                                                   v.transpose(1, 2), is_causal=True)
+            else:        # decode: one query over the whole static cache, masked past `pos`
+                a = F.scaled_dot_product_attention(q.transpose(1, 2),
+                                                   self.k_cache[l].transpose(1, 2),
+                                                   self.v_cache[l].transpose(1, 2),
+                                                   attn_mask=mask)
+            a = a.transpose(1, 2)
+        return F.linear(a.reshape(b, s, nh * hd), self.wo[l])
+
     def _layer(self, l, x, cos, sin, write_pos, mask, causal):
         cfg = self.cfg
-        b, s, d = x.shape
-        nh, hd = cfg.heads, cfg.head_dim
-        h = _rms_norm(x, self.norm1[l], cfg.eps)
-        qkv = F.linear(h, self.wqkv[l]).view(b, s, 3, nh, hd).permute(2, 0, 3, 1, 4)
-        qk = self._rope(qkv[:2], cos, sin)  # q and k rotated in one pass
-        q, k, v = qk[0], qk[1], qkv[2]
-        self.k_cache[l].index_copy_(2, write_pos, k)
-        self.v_cache[l].index_copy_(2, write_pos, v)
-        if causal:   # prefill: attend inside the prompt only
-            a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        else:        # decode: one query over the whole static cache, masked past `pos`
-            a = F.scaled_dot_product_attention(q, self.k_cache[l], self.v_cache[l], attn_mask=mask)
-        x = x + F.linear(a.transpose(1, 2).reshape(b, s, nh * hd), self.wo[l])
+        x = x + self._attention(l, _rms_norm(x, self.norm1[l], cfg.eps), cos, sin, write_pos,
+                                mask, causal)
         return x + self._ffn(l, _rms_norm(x, self.norm2[l], cfg.eps))
+
+    def _add_norm(self, x, delta, w):
+        """``(x + delta, rmsnorm(x + delta) * w)``: one library kernel on the GPU."""
+        if x.is_cuda and self.fused_norm:
+            return norm.residual_rmsnorm(x, delta, w, self.cfg.eps, inplace=True)
+        if delta is not None:
+            x = x + delta
+        return x, _rms_norm(x, w, self.cfg.eps)
 
     # -- prefill / decode ---------------------------------------------------------
     @torch.no_grad()
@@ -170,13 +229,14 @@ class SparseDecoder(nn.Module):
             raise ValueError("prompt does not fit this decoder's batch / max_seq")
         x = self.embed[prompt_ids]
         wp = self.arange[:s]
-        cos, sin = self.cos[:s], self.sin[:s]
+        cos, sin = self.cos[:s].view(s, 1, 1, -1), self.sin[:s].view(s, 1, 1, -1)
         for l in range(self.cfg.layers):
             x = self._layer(l, x, cos, sin, wp, None, True)
         logits = F.linear(_rms_norm(x[:, -1], self.final_norm, self.cfg.eps), self.lm_head).float()
         self.last_logits.copy_(logits)
         self.ids.copy_(logits.argmax(-1))
         self.pos.fill_(s)
+        self.seqlens.fill_(s)
         self.step.zero_()
         self.host_pos, self.host_step = s, 0
         self.generated[0].copy_(self.ids)
@@ -185,15 +245,26 @@ class SparseDecoder(nn.Module):
     def _decode_body(self) -> None:
         pos = self.pos
         x = self.embed[self.ids].unsqueeze(1)                                   # [B, 1, D]
-        cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
-        mask = torch.zeros(1, 1, 1, self.cfg.max_seq, dtype=x.dtype, device=self.dev)
-        mask.masked_fill_((self.arange > pos).view(1, 1, 1, -1), float("-inf"))
+        cos = sin = mask = None
+        if self.attn != "flash":
+            cos = self.cos.index_select(0, pos).view(1, 1, 1, -1)
+            sin = self.sin.index_select(0, pos).view(1, 1, 1, -1)
+            mask = torch.zeros(1, 1, 1, self.cfg.max_seq, dtype=x.dtype, device=self.dev)
+            mask.masked_fill_((self.arange > pos).view(1, 1, 1, -1), float("-inf"))
+        # residual stream x and the sub-block output not yet added to it (delta): every
+        # "add, then normalise" pair is one kernel
+        delta = None
         for l in range(self.cfg.layers):
-            x = self._layer(l, x, cos, sin, pos, mask, False)
-        logits = F.linear(_rms_norm(x[:, 0], self.final_norm, self.cfg.eps), self.lm_head).float()
+            x, h = self._add_norm(x, delta, self.norm1[l])
+            x, h = self._add_norm(x, self._attention(l, h, cos, sin, pos, mask, False),
+                                  self.norm2[l])
+            delta = self._ffn(l, h)
+        x, h = self._add_norm(x, delta, self.final_norm)
+        logits = F.linear(h[:, 0], self.lm_head).float()
         self.last_logits.copy_(logits)
         self.ids.copy_(logits.argmax(-1))
         self.pos.add_(1)
+        self.seqlens.add_(1)
         self.step.add_(1)
         self.generated.index_copy_(0, self.step, self.ids.unsqueeze(0))
 
@@ -202,6 +273,7 @@ class SparseDecoder(nn.Module):
         precede the capture are undone (position and token restored; the cache rows they wrote
         are overwritten by the replays)."""
         ids0, pos0, step0 = self.ids.clone(), self.pos.clone(), self.step.clone()
+        len0 = self.seqlens.clone()
         s = torch.cuda.Stream(self.dev)
         s.wait_stream(torch.cuda.current_stream(self.dev))
         with torch.cuda.stream(s):
@@ -216,6 +288,7 @@ class SparseDecoder(nn.Module):
         self.ids.copy_(ids0)
         self.pos.copy_(pos0)
         self.step.copy_(step0)
+        self.seqlens.copy_(len0)
         self.graph = g
 
     @torch.no_grad()

@@ -56,6 +56,8 @@ def main() -> None:
                     help="1: size the dense tail from the overflow rows seen on earlier calls "
                          "(sparse_ops.set_tail_rows_adaptive); 0: always tail_rows_regular rows")
     ap.add_argument("--tail-rows", type=int, default=2048)
+    ap.add_argument("--wgrad", default="auto", choices=["auto", "sparse", "dense"],
+                    help="weight-gradient form (sparse_ops.set_weight_gradient_mode)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -66,6 +68,7 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=dev)
     sparse_ops.register_ops()
     sparse_ops.set_tail_rows_adaptive(bool(args.adaptive_tail))
+    sparse_ops.set_weight_gradient_mode(args.wgrad)
     torch.ops.sparse_ops_config.set_tail_rows_regular(args.tail_rows)
     b, s, d, h = args.batch, args.seq, args.d_model, args.d_ff
     ffn = synthetic.make_ffn(d, h, seed=21, density=args.density, skew_sigma=1.0)

@@ -20,7 +20,6 @@ pybind extension.  Differences a caller can observe:
 """
 from __future__ import annotations
 
-import abc
 import ctypes
 import os
 from pathlib import Path
@@ -806,17 +805,23 @@ class GatedT2DLinear(nn.Module):
         return OUT
 
 
-class _BaseTwELLMLP(nn.Module, abc.ABC):
-    """Shared base class for fused TwELL MLP wrappers.
+class _BaseTwELLMLP(nn.Module):
+    """What the two fused MLP modules share: weight buffers, lazily created per-layer state,
+    and one forward that picks the functional entry point from (shared slab, in place).
 
-    Built on CPU and moved with ``.to(device).to(dtype)``
-    (benchmark_inference.py:208-213): the weights are registered buffers and the
-    per-layer state is created on the first forward (reference: twell.py:823-834).
+    The modules are built on CPU and moved with ``.to(device).to(dtype)``
+    (benchmark_inference.py:208-213), so the cached layer - which holds a reference to the
+    first-projection weight - is created at the first forward and re-created whenever that
+    buffer has been moved or cast since.  Subclasses name the first-projection buffer
+    (``_first``), their four functional entry points (``_entry``) and the arguments those take
+    between ``A`` and the packed buffer (``_call_args``).
     """
 
-    def __init__(self, layer_number: int, B: torch.Tensor, *, inplace: bool = False,
-                 preallocate_shared_hidden_state: bool = False, compression_factor: int = 8,
-                 ext=None):
+    _first: str = ""
+    _entry: dict = {}
+
+    def __init__(self, layer_number: int, *, inplace: bool, preallocate_shared_hidden_state: bool,
+                 compression_factor: int, ext=None):
         super().__init__()
         self.layer_number = int(layer_number)
         self.ext = ext
@@ -824,41 +829,27 @@ class _BaseTwELLMLP(nn.Module, abc.ABC):
         self.preallocate_shared_hidden_state = bool(preallocate_shared_hidden_state)
         self.compression_factor = _validate_compression_factor(compression_factor)
         self._gate_bias: torch.Tensor | None = None
-        if B.is_cuda:
-            self.layer: D2TLayer | None = D2TLayer(
-                layer_number=self.layer_number, B=B,
-                compression_factor=self.compression_factor, ext=self.ext)
-        else:
-            self.layer = None
-        self._forward_impl = None
-        self._runtime_forward = None
+        self.layer: D2TLayer | None = None
 
-    @abc.abstractmethod
-    def _select_forward_impl(self):
+    def _call_args(self) -> tuple[tuple, dict]:
         raise NotImplementedError
 
-    @abc.abstractmethod
-    def _get_d2t_weight(self) -> torch.Tensor:
-        raise NotImplementedError
+    def _apply_dense_route(self) -> None:  # gated modules override
+        pass
 
-    def _finalize_runtime_forward(self) -> None:
-        self._runtime_forward = (
-            self._forward_impl if self.layer is not None else self._initialize_and_forward)
-
-    def _initialize_and_forward(self, A: torch.Tensor) -> torch.Tensor:
-        B = self._get_d2t_weight()
-        if not B.is_cuda:
+    def _ensure_layer(self) -> None:
+        weight = getattr(self, self._first)
+        entry = _D2T_LAYERS.get(self.layer_number)
+        if (self.layer is not None and entry is not None
+                and entry["B"].data_ptr() == weight.data_ptr()):
+            return
+        if not weight.is_cuda:
             raise RuntimeError("TwELL MLP weights must be moved to CUDA before first forward")
-        self.layer = D2TLayer(layer_number=self.layer_number, B=B,
+        self.layer = D2TLayer(layer_number=self.layer_number, B=weight,
                               compression_factor=self.compression_factor, ext=self.ext)
         if self._gate_bias is not None:
             set_d2t_layer_bias(self.layer_number, self._gate_bias)
         self._apply_dense_route()
-        self._runtime_forward = self._forward_impl
-        return self._forward_impl(A)
-
-    def _apply_dense_route(self) -> None:  # gated modules override
-        pass
 
     def set_gate_bias(self, bias: torch.Tensor | None) -> None:
         """Extension: per-neuron bias added before the ReLU (None = reference behaviour)."""
@@ -867,13 +858,16 @@ class _BaseTwELLMLP(nn.Module, abc.ABC):
             set_d2t_layer_bias(self.layer_number, self._gate_bias)
 
     def forward(self, A: torch.Tensor) -> torch.Tensor:
-        A_shape = A.shape
-        # The cached layer holds a reference to the weight buffer: re-create it if
-        # the module was moved or cast after the first forward.
-        if self.layer is not None and _layer_is_stale(self.layer_number, self._get_d2t_weight()):
-            self.layer = None
-            self._runtime_forward = self._initialize_and_forward
-        return self._runtime_forward(A.view(-1, A_shape[-1])).view(A_shape)
+        shape = A.shape
+        rows = A.view(-1, shape[-1])
+        self._ensure_layer()
+        shared = self.preallocate_shared_hidden_state
+        args, kwargs = self._call_args()
+        if shared:  # one slab for all layers of the process (they run one after another)
+            args = args + (self.layer.prepare_shared_hidden_state(rows),)
+        out = self._entry[(shared, self.inplace)](self.layer_number, rows, *args, ext=self.ext,
+                                                  **kwargs)
+        return A if self.inplace else out.view(shape)
 
     def destroy(self) -> None:
         if self.layer is not None:
@@ -881,7 +875,6 @@ class _BaseTwELLMLP(nn.Module, abc.ABC):
             self.layer = None
         if self.preallocate_shared_hidden_state:
             _clear_shared_packed_hidden_state()
-        self._runtime_forward = self._initialize_and_forward
 
     def __del__(self):
         try:
@@ -890,89 +883,60 @@ class _BaseTwELLMLP(nn.Module, abc.ABC):
             pass
 
 
-def _layer_is_stale(layer_number: int, weight: torch.Tensor) -> bool:
-    entry = _D2T_LAYERS.get(int(layer_number))
-    return entry is None or entry["B"].data_ptr() != weight.data_ptr()
-
-
 class TwELLMLP(_BaseTwELLMLP):
     """Fused non-gated TwELL MLP wrapper."""
+
+    _first = "UP"
+    _entry = {(False, False): run_mlp_layer, (False, True): run_mlp_layer_inplace,
+              (True, False): _run_mlp_layer_with_hidden_states,
+              (True, True): _run_mlp_layer_inplace_with_hidden_states}
 
     def __init__(self, layer_number: int, UP: torch.Tensor, DOWN: torch.Tensor,
                  num_splits: int = 2, inplace: bool = False,
                  preallocate_shared_hidden_state: bool = False, compression_factor: int = 8,
                  ext=None):
-        compression_factor = _validate_compression_factor(compression_factor)
-        if compression_factor != 8:
+        if _validate_compression_factor(compression_factor) != 8:
             raise ValueError("Only compression_factor=8 is currently supported for TwELLMLP")
-        up = UP.contiguous()
-        down = DOWN.contiguous()
-        super().__init__(layer_number=layer_number, B=up, inplace=inplace,
+        super().__init__(layer_number, inplace=inplace,
                          preallocate_shared_hidden_state=preallocate_shared_hidden_state,
                          compression_factor=compression_factor, ext=ext)
-        self.register_buffer("UP", up)
-        self.register_buffer("DOWN", down)
+        self.register_buffer("UP", UP.contiguous())
+        self.register_buffer("DOWN", DOWN.contiguous())
         self.num_splits = int(num_splits)
-        self._forward_impl = self._select_forward_impl()
-        self._finalize_runtime_forward()
 
-    def _get_d2t_weight(self) -> torch.Tensor:
-        return self.UP
-
-    def _select_forward_impl(self):
-        if self.preallocate_shared_hidden_state:
-            return self._forward_shared_inplace if self.inplace else self._forward_shared
-        return self._forward_temporary_inplace if self.inplace else self._forward_temporary
-
-    def _forward_temporary(self, A: torch.Tensor) -> torch.Tensor:
-        return run_mlp_layer(self.layer.layer_number, A, self.DOWN,
-                             num_splits=self.num_splits, ext=self.ext)
-
-    def _forward_temporary_inplace(self, A: torch.Tensor) -> torch.Tensor:
-        run_mlp_layer_inplace(self.layer.layer_number, A, self.DOWN,
-                              num_splits=self.num_splits, ext=self.ext)
-        return A
-
-    def _forward_shared(self, A: torch.Tensor) -> torch.Tensor:
-        return _run_mlp_layer_with_hidden_states(
-            self.layer.layer_number, A, self.DOWN, self.layer.prepare_shared_hidden_state(A),
-            num_splits=self.num_splits, ext=self.ext)
-
-    def _forward_shared_inplace(self, A: torch.Tensor) -> torch.Tensor:
-        _run_mlp_layer_inplace_with_hidden_states(
-            self.layer.layer_number, A, self.DOWN, self.layer.prepare_shared_hidden_state(A),
-            num_splits=self.num_splits, ext=self.ext)
-        return A
+    def _call_args(self):
+        return (self.DOWN,), {"num_splits": self.num_splits}
 
 
 class TwELLGatedMLP(_BaseTwELLMLP):
     """Fused gated TwELL MLP wrapper."""
 
+    _first = "GATE"
+    _entry = {(False, False): run_gated_mlp_layer, (False, True): run_gated_mlp_layer_inplace,
+              (True, False): _run_gated_mlp_layer_with_hidden_states,
+              (True, True): _run_gated_mlp_layer_inplace_with_hidden_states}
+
     def __init__(self, layer_number: int, GATE: torch.Tensor, UP: torch.Tensor,
                  DOWN: torch.Tensor, inplace: bool = False,
                  preallocate_shared_hidden_state: bool = False, highest_precision: bool = False,
                  compression_factor: int = 8, flex_kernels: bool = False, ext=None):
-        compression_factor = _validate_compression_factor(compression_factor)
-        if compression_factor != 8 and not flex_kernels:
+        if _validate_compression_factor(compression_factor) != 8 and not flex_kernels:
             raise ValueError("compression_factor != 8 requires flex_kernels=True")
-        gate = GATE.contiguous()
-        up = UP.contiguous()
-        down = DOWN.contiguous()
-        super().__init__(layer_number=layer_number, B=gate, inplace=inplace,
+        super().__init__(layer_number, inplace=inplace,
                          preallocate_shared_hidden_state=preallocate_shared_hidden_state,
                          compression_factor=compression_factor, ext=ext)
         self.highest_precision = bool(highest_precision)
         self.flex_kernels = bool(flex_kernels)
-        self.register_buffer("GATE", gate)
-        self.register_buffer("UP", up)
-        self.register_buffer("DOWN", down)
+        self.register_buffer("GATE", GATE.contiguous())
+        self.register_buffer("UP", UP.contiguous())
+        self.register_buffer("DOWN", DOWN.contiguous())
         self._dense_route: dict | None = None
         self._down_t: torch.Tensor | None = None
-        self._forward_impl = self._select_forward_impl()
-        self._finalize_runtime_forward()
 
-    def _get_d2t_weight(self) -> torch.Tensor:
-        return self.GATE
+    def _call_args(self):
+        return (self.UP, self.DOWN), {"highest_precision": self.highest_precision,
+                                      "compression_factor": self.compression_factor,
+                                      "flex_kernels": self.flex_kernels}
 
     def enable_dense_route(self, dense_cap: int | None = None, nnz_threshold: int | None = None,
                            min_tokens: int = 256, dense_all_tokens: int | None = None) -> None:
@@ -1000,40 +964,3 @@ class TwELLGatedMLP(_BaseTwELLMLP):
         if self._down_t is None or self._down_t.device != self.DOWN.device:
             self._down_t = self.DOWN.t().contiguous()
         set_d2t_layer_dense_route(self.layer_number, self._down_t, **self._dense_route)
-
-    def _select_forward_impl(self):
-        if self.preallocate_shared_hidden_state:
-            return self._forward_shared_inplace if self.inplace else self._forward_shared
-        return self._forward_temporary_inplace if self.inplace else self._forward_temporary
-
-    def _forward_temporary(self, A: torch.Tensor) -> torch.Tensor:
-        return run_gated_mlp_layer(
-            self.layer.layer_number, A, self.UP, self.DOWN,
-            highest_precision=self.highest_precision,
-            compression_factor=self.compression_factor, flex_kernels=self.flex_kernels,
-            ext=self.ext)
-
-    def _forward_temporary_inplace(self, A: torch.Tensor) -> torch.Tensor:
-        run_gated_mlp_layer_inplace(
-            self.layer.layer_number, A, self.UP, self.DOWN,
-            highest_precision=self.highest_precision,
-            compression_factor=self.compression_factor, flex_kernels=self.flex_kernels,
-            ext=self.ext)
-        return A
-
-    def _forward_shared(self, A: torch.Tensor) -> torch.Tensor:
-        return _run_gated_mlp_layer_with_hidden_states(
-            self.layer.layer_number, A, self.UP, self.DOWN,
-            self.layer.prepare_shared_hidden_state(A),
-            highest_precision=self.highest_precision,
-            compression_factor=self.compression_factor, flex_kernels=self.flex_kernels,
-            ext=self.ext)
-
-    def _forward_shared_inplace(self, A: torch.Tensor) -> torch.Tensor:
-        _run_gated_mlp_layer_inplace_with_hidden_states(
-            self.layer.layer_number, A, self.UP, self.DOWN,
-            self.layer.prepare_shared_hidden_state(A),
-            highest_precision=self.highest_precision,
-            compression_factor=self.compression_factor, flex_kernels=self.flex_kernels,
-            ext=self.ext)
-        return A

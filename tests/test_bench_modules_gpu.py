@@ -43,8 +43,8 @@ def test_sweep_bench_small():
 
 def test_training_bench_small():
     recs = run_module("sparser_faster_llms_b200.training_bench", "--batch", "2", "--seq", "256",
-                      "--d-model", "512", "--d-ff", "1024", "--density", "0.03", "--reps", "2",
-                      "--warmup", "1")
+                      "--d-model", "512", "--d-ff", "1024", "--density", "0.03", "--reps", "3",
+                      "--warmup", "4")  # the warm-up also loads the tail GEMMs' library kernels
     assert len(recs) == 1
     r = recs[0]
     assert r["tokens"] == 512 and r["l0_per_token"] > 0

