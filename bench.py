@@ -63,6 +63,8 @@ def parse():
     ap.add_argument("--d-ff", type=int, default=D_FF)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-decode-model", action="store_true",
+                    help="skip the end-to-end decode ms/token of the full 1.5B-shape model")
     ap.add_argument("--no-energy", action="store_true",
                     help="skip the energy-per-step measurement (single GPU only)")
     ap.add_argument("--energy-seconds", type=float, default=1.5,
@@ -424,6 +426,9 @@ def run_ours(args):
 
     if not args.no_e2e:
         result["e2e"] = run_e2e(args, layers, x, device, dist_on, par)
+    if (not dist_on and not args.no_decode_model and not args.no_graph
+            and (args.layers, args.d_model, args.d_ff) == (LAYERS, D_MODEL, D_FF)):
+        result["config"]["decode_ms_per_token"] = decode_model_ms_per_token()
     if dist_on and rank == 0:
         # self-check of the sharded sum: layer 0 recomputed on this rank alone over all of d_ff
         wf = full_layer_weights(args, device, 0).to(torch.bfloat16).contiguous()
@@ -460,6 +465,24 @@ def run_ours(args):
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
+
+
+def decode_model_ms_per_token():
+    """End-to-end decode of the full random-init 1.5B-shape model (attention, norms, LM head
+    around the FFN; decode_model.py): ms per token with the TwELL FFN and with the dense cuBLAS
+    FFN on the same weights, prompt 512, 64 timed steps of one CUDA graph each."""
+    from sparser_faster_llms_b200 import decode_model as dm
+    cfg = dm.DecoderConfig(max_seq=640)
+    out = {}
+    for b in (1, 8, 32):
+        try:
+            tw = dm.time_decode(cfg, b, 512, 72, "twell", reps=1)
+            de = dm.time_decode(cfg, b, 512, 72, "dense", reps=1)
+            out[str(b)] = {"twell_ffn": tw["ms_per_token"], "dense_cublas_ffn": de["ms_per_token"],
+                           "ratio": de["ms_per_token"] / tw["ms_per_token"]}
+        except Exception as exc:  # the model leg must never cost the benchmark line
+            out[str(b)] = {"unavailable": f"{type(exc).__name__}: {exc}"[:160]}
+    return out
 
 
 def run_e2e(args, layers, x, device, dist_on, par=None):

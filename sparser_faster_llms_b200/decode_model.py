@@ -87,7 +87,11 @@ class SparseDecoder(nn.Module):
         bf = torch.bfloat16
         d, hd, nh = cfg.d_model, cfg.head_dim, cfg.heads
 
+        dgen = torch.Generator(device=dev).manual_seed(seed) if dev.type == "cuda" else None
+
         def w(*shape):
+            if dgen is not None:  # drawn on the device: a model-sized stack builds in a second
+                return (torch.randn(*shape, generator=dgen, device=dev) * 0.02).to(bf)
             return (torch.randn(*shape, generator=gen) * 0.02).to(bf).to(dev)
 
         self.embed = w(cfg.vocab, d)
@@ -100,7 +104,8 @@ class SparseDecoder(nn.Module):
         self.ffns = nn.ModuleList()
         for l in range(cfg.layers):
             f = synthetic.make_ffn(d, cfg.d_ff, seed=seed * 1000 + l, density=cfg.density,
-                                   skew_sigma=cfg.skew_sigma, fold_bias=False)
+                                   skew_sigma=cfg.skew_sigma, fold_bias=False, device=dev,
+                                   generate_on_device=True)
             if self.shard is not None:
                 from . import sharded
                 r, w = self.shard["rank"], self.shard["world"]

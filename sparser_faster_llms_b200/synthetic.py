@@ -43,18 +43,26 @@ def neuron_rates(h: int, density: float, skew_sigma: float, gen: torch.Generator
 
 def make_ffn(d_model: int, d_ff: int, *, seed: int = 0, density: float = 0.02,
              skew_sigma: float = 0.0, fold_bias: bool = True, std: float = 0.02,
-             dtype: torch.dtype = torch.bfloat16, device="cpu") -> SparseFFN:
+             dtype: torch.dtype = torch.bfloat16, device="cpu",
+             generate_on_device: bool = False) -> SparseFFN:
+    """``generate_on_device`` draws the three matrices with the device's own generator (much
+    faster for model-sized stacks; another random stream than the CPU one, same statistics)."""
     gen = torch.Generator().manual_seed(seed)
-    gate = torch.randn(d_ff, d_model, generator=gen) * std
-    up = torch.randn(d_ff, d_model, generator=gen) * std
-    down = torch.randn(d_ff, d_model, generator=gen) * std
+    if generate_on_device and torch.device(device).type == "cuda":
+        dgen = torch.Generator(device=device).manual_seed(seed)
+        gate, up, down = (torch.randn(d_ff, d_model, generator=dgen, device=device) * std
+                          for _ in range(3))
+    else:
+        gate = torch.randn(d_ff, d_model, generator=gen) * std
+        up = torch.randn(d_ff, d_model, generator=gen) * std
+        down = torch.randn(d_ff, d_model, generator=gen) * std
     rates = neuron_rates(d_ff, density, skew_sigma, gen)
     k_eff = d_model - 1 if fold_bias else d_model
     sigma = std * math.sqrt(k_eff)  # std of the pre-activation for x ~ N(0, 1)
     shift = (sigma * torch.special.ndtri(rates)).to(torch.float32)
     bias = None
     if fold_bias:
-        gate[:, 0] = shift
+        gate[:, 0] = shift.to(gate.device)
     else:
         bias = shift.to(device)
     return SparseFFN(gate.to(dtype).to(device), up.to(dtype).to(device),
