@@ -477,10 +477,15 @@ int launch_t2d(const void* x, const void* packed, const void* up, const void* do
       }
       max_clusters[dev][slot] = n;
     }
-    if (M * nc > (int64_t)max_clusters[dev][slot])
-      return fail(B200_EUNSUPPORTED,
-                  "twell_t2d: the fused all-reduce needs all %lld clusters of %d CTAs resident at "
-                  "once (limit %d)", (long long)(M * nc), cs, max_clusters[dev][slot]);
+    if (M * nc > (int64_t)max_clusters[dev][slot]) {
+      // fewer clusters per token until the grid fits one wave
+      nc = (int)((int64_t)max_clusters[dev][slot] / M);
+      if (nc < 1)
+        return fail(B200_EUNSUPPORTED,
+                    "twell_t2d: the fused all-reduce needs all %lld clusters of %d CTAs resident "
+                    "at once (limit %d)", (long long)M, cs, max_clusters[dev][slot]);
+      cfg.gridDim = dim3((unsigned)(M * nc * cs), 1, 1);
+    }
   }
   cfg.numAttrs = add_pdl_attribute(attr, 1, 2);
   cudaError_t e = cudaLaunchKernelEx(
@@ -570,16 +575,26 @@ int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, con
   unsigned int* counters = reinterpret_cast<unsigned int*>(workspace);
   float* partial = workspace ? reinterpret_cast<float*>(counters + kCounterWords) : nullptr;
   const int ni = (int)(D / 256);
-  if (gated) {
-    return hp ? dispatch_ni<true, true>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                        counters, skip_rows, far, stream)
-              : dispatch_ni<true, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                         counters, skip_rows, far, stream);
+  auto run = [&](int cs_, int nc_) {
+    if (gated) {
+      return hp ? dispatch_ni<true, true>(ni, x, packed, up, down, out, M, H, cf, cs_, nc_, partial,
+                                          counters, skip_rows, far, stream)
+                : dispatch_ni<true, false>(ni, x, packed, up, down, out, M, H, cf, cs_, nc_,
+                                           partial, counters, skip_rows, far, stream);
+    }
+    return hp ? dispatch_ni<false, true>(ni, x, packed, up, down, out, M, H, cf, cs_, nc_, partial,
+                                         counters, skip_rows, far, stream)
+              : dispatch_ni<false, false>(ni, x, packed, up, down, out, M, H, cf, cs_, nc_,
+                                          partial, counters, skip_rows, far, stream);
+  };
+  int rc = run(cs, nc);
+  // A fused call whose clusters are not all resident at once is retried with smaller clusters
+  // (one cluster per token): wide d_model means 512-thread CTAs, one per SM.
+  while (rc == B200_EUNSUPPORTED && far.world > 1 && cs > 1) {
+    cs /= 2;
+    rc = run(cs, 1);
   }
-  return hp ? dispatch_ni<false, true>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                       counters, skip_rows, far, stream)
-            : dispatch_ni<false, false>(ni, x, packed, up, down, out, M, H, cf, cs, nc, partial,
-                                        counters, skip_rows, far, stream);
+  return rc;
 }
 
 int sm_count();  // c_api.cu

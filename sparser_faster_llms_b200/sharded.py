@@ -146,6 +146,7 @@ class ShardedTwELLGatedMLP(nn.Module):
             local_factory = TwELLGatedMLP
         self.local = local_factory(layer_number, g, u, d, **twell_kwargs)
         self.reduce_dtype = reduce_dtype
+        self.last_route = None  # how the last forward summed the shards: fused / peer / nccl
 
     def _fused_ready(self, A: torch.Tensor) -> bool:
         """Attach the fused all-reduce to the local layer's cached state (created on the first
@@ -166,6 +167,7 @@ class ShardedTwELLGatedMLP(nn.Module):
     def forward(self, A: torch.Tensor) -> torch.Tensor:
         if self._fused_ready(A):
             try:
+                self.last_route = "fused"
                 return self.local(A)  # the contraction's epilogue has already summed the shards
             except ValueError as exc:
                 # the library refuses a fused call whose grid is not resident at once (the same
@@ -181,7 +183,9 @@ class ShardedTwELLGatedMLP(nn.Module):
         par = self.peer_allreduce
         if (self.world_size > 1 and par is not None
                 and y.numel() * y.element_size() <= getattr(par, "max_bytes", float("inf"))):
+            self.last_route = "peer"
             return par.all_reduce(y.contiguous())  # larger outputs (prefill) go through NCCL
+        self.last_route = "nccl" if self.world_size > 1 else "local"
         if self.world_size > 1:
             if self.reduce_dtype is not None and self.reduce_dtype != y.dtype:
                 acc = y.to(self.reduce_dtype)

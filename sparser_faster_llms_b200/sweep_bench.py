@@ -145,7 +145,8 @@ def sharded_sweep(args) -> None:
                 t = torch.tensor([_time(lambda: mod(x), reps)], device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 rec = {"tokens": m, "density": rho, "skew": skew, "d_model": d, "d_ff": h,
-                       "n_gpus": world, "sharded_sparse_us": float(t.item())}
+                       "n_gpus": world, "sharded_sparse_us": float(t.item()),
+                       "shard_sum": mod.last_route}
                 if rank == 0:
                     def cublas():
                         return (torch.relu(x @ g.T) * (x @ u.T)) @ dn
