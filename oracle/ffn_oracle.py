@@ -236,12 +236,14 @@ def slab_active_rows(p_slab: np.ndarray, vals_slab: np.ndarray | None, output_n:
                      compression_factor: int = 8) -> np.ndarray:
     """Per-neuron count of rows whose stored value is not +-0, read from slab arrays (the
     pattern ``p_slab`` gives the columns, ``vals_slab`` the values when given).  Entries a
-    slab dropped on overflow are not seen, as on the device."""
+    slab dropped on overflow are not seen, as on the device; neither are rows whose count
+    words carry the sign bit (the training operator's mark for "this row went to the dense
+    tail": every kernel reads such a count as zero)."""
     w = tf.slab_words(compression_factor)
     tiles = output_n // TILE_N
     p = np.ascontiguousarray(p_slab).view(np.uint32).reshape(-1, tiles, w)
     v = p if vals_slab is None else np.ascontiguousarray(vals_slab).view(np.uint32).reshape(p.shape)
-    cnt = np.clip(p[:, :, 0].astype(np.int64), 0, w - 1)
+    cnt = np.clip(p[:, :, 0].view(np.int32).astype(np.int64), 0, w - 1)
     stored = np.arange(1, w)[None, None, :] <= cnt[:, :, None]
     nonzero = ((v[:, :, 1:] >> 16) & 0x7FFF) != 0
     cols = (p[:, :, 1:] & 0xFFFF)[stored & nonzero]

@@ -110,12 +110,14 @@ def _wgrad_workspace(dev: torch.device, m: int, d: int, h: int) -> torch.Tensor:
 
 def set_tail_rows_adaptive(on: bool) -> None:
     """Size the dense tail from the overflow-row count seen on earlier calls with the same
-    gate matrix (read back asynchronously, never waited for): twice the last count, at least
-    128 rows, at most ``tail_rows_regular``.  Off (the default) the tail always spans
-    ``min(tail_rows_regular, tokens)`` rows, which is what the reference's forward computes
-    (custom_op.cpp:125-127 sets the active rows to the capacity).  With a sudden jump in
-    overflow rows the excess rows of that one call fall back to the slab prefix and are
-    counted in ``dropped``.  No reference counterpart."""
+    gate matrix (read back asynchronously, never waited for): twice the last count rounded up
+    to 128 rows, at most ``tail_rows_regular`` - and no tail at all while the last count is
+    zero (the call then only counts its overflow rows, so that the next one has a tail).  Off
+    (the default) the tail always spans ``min(tail_rows_regular, tokens)`` rows, which is what
+    the reference's forward computes (custom_op.cpp:125-127 sets the active rows to the
+    capacity).  The price of the adaptive form: the first call in which overflow rows appear,
+    or more than doubles, leaves the excess rows on their slab prefix for that one call
+    (counted in ``dropped``).  No reference counterpart."""
     _CONFIG["tail_rows_adaptive"] = 1 if on else 0
 
 
@@ -129,7 +131,7 @@ def _tail_state(key: tuple) -> dict:
         if len(_TAIL_SEEN) > 512:
             _TAIL_SEEN.clear()
         st = {"host": torch.zeros((), dtype=torch.int64).pin_memory(),
-              "event": None, "last": None, "cap_fwd": 0}
+              "event": None, "last": None, "cap_fwd": None}
         _TAIL_SEEN[key] = st
     return st
 
@@ -145,8 +147,9 @@ def _tail_capacity(key: tuple, m: int) -> int:
     if st["event"] is not None and st["event"].query():
         st["last"] = int(st["host"].item())
     if st["last"] is not None:
-        cap = min(cap, max(128, (2 * st["last"] + 127) // 128 * 128))
-    st["cap_fwd"] = max(st["cap_fwd"], cap)  # the backward must span at least this many rows
+        cap = 0 if st["last"] == 0 else min(cap, (2 * st["last"] + 127) // 128 * 128)
+    # the backward must span at least the rows of every forward since the last backward
+    st["cap_fwd"] = cap if st["cap_fwd"] is None else max(st["cap_fwd"], cap)
     return cap
 
 
@@ -269,16 +272,19 @@ def ff_forward_impl(X: torch.Tensor, G: torch.Tensor, K: torch.Tensor, V: torch.
                       m, d, h, cf)
         inv_m = 1.0 / max(m, 1)
         tail = None
-        if cap > 0:
-            # rows with an overflowed tile leave the slabs: flag their count words
+        adaptive = bool(_CONFIG["tail_rows_adaptive"]) and m > 0 and \
+            not _CONFIG["discard_overflow"] and _CONFIG["tail_rows_regular"] > 0
+        if cap > 0 or adaptive:
             cnt = _count_view(P, m, h, cf)
             over = (cnt > TILE // cf - 1).any(dim=1)
+            if adaptive:
+                _tail_observe(tail_key, over.sum())
+        if cap > 0:
+            # rows with an overflowed tile leave the slabs: flag their count words
             in_tail = over & (over.cumsum(0) <= cap) if cap < m else over
             l0 = cnt.sum(dtype=torch.float32) * inv_m
             cnt.bitwise_or_(in_tail.to(torch.int32).mul_(_INT_MIN).unsqueeze(1))
             tail = _tail_index(in_tail, cap, m)
-            if _CONFIG["tail_rows_adaptive"]:
-                _tail_observe(tail_key, over.sum())
         R = torch.empty_like(P)
         T = torch.empty_like(P)
         row_l1 = torch.empty(m, dtype=torch.float32, device=dev)
@@ -349,11 +355,12 @@ def ff_backward_impl(X, G, K, V, P, R, T, gR, gl0, gl1):
         cap = min(int(_CONFIG["tail_rows_regular"]), m)
         if _CONFIG["tail_rows_adaptive"]:
             st = _TAIL_SEEN.get((dev.index, G.data_ptr(), m, h))
-            if st is not None and st["cap_fwd"] > 0:
+            if st is not None and st["cap_fwd"] is not None:
                 cap = min(cap, st["cap_fwd"])  # what the forward(s) since the last backward used
-                st["cap_fwd"] = 0
-        flagged = (_count_view(P, m, h, cf) < 0).any(dim=1)
-        tail = _tail_index(flagged, cap, m)
+                st["cap_fwd"] = None
+        if cap > 0:
+            flagged = (_count_view(P, m, h, cf) < 0).any(dim=1)
+            tail = _tail_index(flagged, cap, m)
     pad = 1 if tail is not None else 0
     with _Timer("ff_backward_gated_total"):
         dR = torch.empty_like(P)

@@ -240,3 +240,29 @@ def test_discard_mode_drops_and_counts_what_the_tail_would_keep():
     finally:
         cfg.set_discard_overflow(0)
         cfg.set_tail_rows_regular(2048)
+
+
+def test_adaptive_tail_costs_nothing_until_overflow_appears_then_catches_up():
+    """Adaptive sizing: while no call has seen an overflowed row there is no tail; the first
+    call that meets overflow rows leaves them on their slab prefix (counted), the next one has
+    a tail and is exact again."""
+    b, s, d, h = 2, 320, 512, 2048
+    ffn, x_mixed, gout, _ = _mixed_density_case(b, s, d, h)
+    x_sparse = synthetic.make_tokens(b * s, d, seed=45).reshape(b, s, d)   # ~3 % everywhere
+    ref_mixed = dense_reference(x_mixed, ffn.gate, ffn.up, ffn.down, gout, 0.0)[0]
+    G, K, V = (t.to(DEV) for t in (ffn.gate, ffn.up, ffn.down))   # one gate tensor = one history
+    sparse_ops.set_tail_rows_adaptive(True)
+    try:
+        for _ in range(3):
+            out, *_, P, _, _ = sparse_ops.ff_forward_gated(x_sparse.to(DEV), G, K, V)
+            torch.cuda.synchronize()
+            assert int(P.overflow_count_tensor().item()) == 0
+        assert not bool((P.slab.view(b * s, h // 256, -1)[:, :, 0] < 0).any())
+        out, *_, P, _, _ = sparse_ops.ff_forward_gated(x_mixed.to(DEV), G, K, V)
+        torch.cuda.synchronize()
+        assert int(P.overflow_count_tensor().item()) > 0          # the one lossy call
+        out, *_, P, _, _ = sparse_ops.ff_forward_gated(x_mixed.to(DEV), G, K, V)
+        torch.cuda.synchronize()
+        assert int(P.overflow_count_tensor().item()) == 0 and rel_l2(out, ref_mixed) < REL_OUT
+    finally:
+        sparse_ops.set_tail_rows_adaptive(False)

@@ -56,7 +56,9 @@ def test_activity_matches_the_oracle_on_the_same_slabs(b, s, d, h, density, widt
     pat = sparse_ops.neuron_activity(P).cpu().numpy()
     assert pat[300:340].sum() > 0                      # in the pattern, zero in T
     # the forward's l0 counts pattern entries per token; so does the activity of P
-    stored = tf.slab_counts(p_np, cf).clip(max=256 // cf - 1).sum()
+    counts = tf.slab_counts(p_np, cf)
+    counts = np.where(counts >= 2 ** 31, 0, counts)    # rows the dense tail took: sign bit set
+    stored = counts.clip(max=256 // cf - 1).sum()
     assert pat.sum() == stored
 
 
