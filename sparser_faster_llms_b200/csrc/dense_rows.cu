@@ -158,7 +158,8 @@ dense_rows_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
                        const __grid_constant__ CUtensorMap tmap_a1,
                        const __grid_constant__ CUtensorMap tmap_b, const float* __restrict__ bias,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ row_ids,
-                       const int* __restrict__ n_rows_ptr, int n_rows_host, int K, int ld_out) {
+                       const int* __restrict__ n_rows_ptr, int n_rows_host, int K, int ld_out,
+                       int group) {
   // KS k-values per stage: 64 (128-byte rows, 128-byte swizzle) or 32 (64-byte rows and swizzle)
   constexpr int kATile = 128 * KS * 2;
   constexpr int kBTileBytes = NTOK * KS * 2;
@@ -168,7 +169,9 @@ dense_rows_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
 
   // row count: on the device when routing decided it, else given by the host
   const int n_rows = n_rows_ptr != nullptr ? *n_rows_ptr : n_rows_host;
-  const int m0 = blockIdx.y * NTOK;
+  int tile, mblk;
+  raster_remap(group, tile, mblk);
+  const int m0 = mblk * NTOK;
   if (m0 >= n_rows) return;  // uniform for the CTA: nothing allocated yet
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -179,7 +182,6 @@ dense_rows_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
   __shared__ volatile int abort_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x;
   const int ksteps = K / KS;
   const int a0_row = DUAL ? tile * 128 : tile * 256;
   const int a1_row = DUAL ? tile * 128 : tile * 256 + 128;
@@ -608,7 +610,7 @@ int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void
       return rc;
     deep<<<grid, kThreadsTc, smem_deep, stream>>>(map_a0, map_a1, map_b, bias,
                                                   static_cast<__nv_bfloat16*>(out), row_ids,
-                                                  n_rows_ptr, (int)cap, (int)K, (int)ld_out);
+                                                  n_rows_ptr, (int)cap, (int)K, (int)ld_out, 1);
     return check_launch("b200_twell_gated_t2d_hybrid (dense rows, deep ring)");
   }
   const size_t smem = (size_t)STAGES * (2 * 128 * KS * 2 + kDenseTok * KS * 2) + 1024;
@@ -617,7 +619,9 @@ int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void
   if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_gated_t2d_hybrid")) return rc;
   kern<<<grid, kThreadsTc, smem, stream>>>(map_a0, map_a1, map_b, bias,
                                            static_cast<__nv_bfloat16*>(out), row_ids, n_rows_ptr,
-                                           (int)cap, (int)K, (int)ld_out);
+                                           (int)cap, (int)K, (int)ld_out,
+                                           raster_group((DUAL ? 2 : 1) * a_rows * K * 2,
+                                                        (int64_t)kDenseTok * K * 2));
   return check_launch("b200_twell_gated_t2d_hybrid (dense rows)");
 }
 

@@ -4,6 +4,7 @@
 // map encoder.  Everything here is file-local to the including translation unit.
 #pragma once
 
+#include <cstdlib>
 #include <cuda.h>
 
 #include "common.cuh"
@@ -152,7 +153,39 @@ __device__ __forceinline__ bool epi_barrier_and(bool v) {
   return r != 0;
 }
 
+// Launch order of a (feature tiles, token blocks) grid.  CTAs start in the order of their linear
+// index; walking that index down `group` token blocks before moving on to the next feature
+// tile keeps the token rows of one group in L2 while the weight matrix streams past once per
+// group instead of once per resident wave.  group <= 1 leaves (blockIdx.x, blockIdx.y) as is.
+__device__ __forceinline__ void raster_remap(int group, int& tile, int& mblk) {
+  tile = (int)blockIdx.x;
+  mblk = (int)blockIdx.y;
+  if (group <= 1) return;
+  const int pid = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  const int per_group = group * (int)gridDim.x;
+  const int first = (pid / per_group) * group;
+  const int rows = min(group, (int)gridDim.y - first);
+  const int in_group = pid - (pid / per_group) * per_group;
+  mblk = first + in_group % rows;
+  tile = in_group / rows;
+}
+
 // ---- host side -------------------------------------------------------------
+// Token blocks per raster group: none while the weight operand (weight_bytes) stays resident in
+// L2 by itself; otherwise as many blocks as put about 32 MB of token rows (block_bytes each)
+// into one group.  B200_TC_RASTER=<n> forces a group size (1 = off).
+inline int raster_group(int64_t weight_bytes, int64_t block_bytes) {
+  static int forced = -2;
+  if (forced == -2) {
+    const char* e = getenv("B200_TC_RASTER");
+    forced = e != nullptr ? atoi(e) : -1;
+  }
+  if (forced >= 1) return forced;
+  if (weight_bytes <= (int64_t)48 << 20) return 1;
+  const int64_t g = ((int64_t)32 << 20) / (block_bytes > 0 ? block_bytes : 1);
+  return (int)(g < 4 ? 4 : g > 64 ? 64 : g);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,

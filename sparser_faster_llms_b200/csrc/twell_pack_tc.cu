@@ -41,7 +41,8 @@ template <int NTOK, int STAGES, int MINB>
 __global__ void __launch_bounds__(kThreadsTc, MINB)
 twell_pack_tc_kernel(const __grid_constant__ CUtensorMap tmap_w,
                      const __grid_constant__ CUtensorMap tmap_x, const float* __restrict__ bias,
-                     uint32_t* __restrict__ packed, int M, int D, int slab_w, int row_words) {
+                     uint32_t* __restrict__ packed, int M, int D, int slab_w, int row_words,
+                     int group) {
   constexpr int kBTileBytes = NTOK * 128;
   constexpr int kStageBytes = 2 * kATileBytes + kBTileBytes;
   constexpr uint32_t kTmemCols = 2 * NTOK;  // 128 or 256: a power of two >= 32
@@ -57,8 +58,9 @@ twell_pack_tc_kernel(const __grid_constant__ CUtensorMap tmap_w,
   __shared__ int prefix_s[32][8];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x;
-  const int m0 = blockIdx.y * NTOK;
+  int tile, mblk;
+  raster_remap(group, tile, mblk);
+  const int m0 = mblk * NTOK;
   const int ksteps = D / kStageK;
 
   if (threadIdx.x == 0) {
@@ -608,7 +610,8 @@ int launch_tc(const void* x, const void* w, const float* bias, void* packed, int
   const int tiles = (int)(H / kTileN);
   dim3 grid((unsigned)tiles, (unsigned)((M + NTOK - 1) / NTOK), 1);
   kern<<<grid, kThreadsTc, smem, stream>>>(map_w, map_x, bias, static_cast<uint32_t*>(packed),
-                                           (int)M, (int)D, slab_w, tiles * slab_w);
+                                           (int)M, (int)D, slab_w, tiles * slab_w,
+                                           raster_group(H * D * 2, (int64_t)NTOK * D * 2));
   return check_launch("b200_twell_pack (tcgen05)");
 }
 
