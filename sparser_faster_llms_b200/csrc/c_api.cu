@@ -53,6 +53,14 @@ int twell_decode_small_launch(bool gated, bool hp, const void* x, const void* w,
                               void* out, int64_t M, int64_t D, int64_t H, int cf, void* workspace,
                               size_t workspace_bytes, cudaStream_t stream);
 int l2_prefetch_launch(const void* p, int64_t bytes, cudaStream_t stream);
+bool twell_gemv_serves(int64_t M, int64_t D, int64_t H);
+size_t twell_gemv_workspace_bytes(int64_t D, int64_t H);
+int twell_gemv_pack(const void* x, const void* w, const float* bias, void* packed, int64_t D,
+                    int64_t H, int cf, cudaStream_t stream);
+int twell_gemv_layer(bool gated, bool hp, const void* x, const void* w, const float* bias,
+                     const void* up, const void* down, void* packed, void* out, int64_t D,
+                     int64_t H, int cf, void* workspace, size_t workspace_bytes,
+                     cudaStream_t stream);
 int twell_decode_status();
 #ifdef B200_TRACE
 void twell_decode_trace(unsigned long long* out16);
@@ -77,6 +85,22 @@ int decode_fused_mode() {
     const char* e = getenv("B200_DECODE_FUSED");
     const int v = e != nullptr ? atoi(e) : B200_DECODE_FUSED_DEFAULT;
     mode = (v == 1 || v == 2) ? v : 0;
+  }
+  return mode;
+}
+
+// One-token calls (environment variable B200_ONE_TOKEN): 0 the few-token kernels as for any
+// other small batch, 1 the GEMV pack kernel, 2 (default) also the whole layer in that kernel when
+// b200_twell_gated_mlp / b200_twell_mlp get a workspace that holds its partial rows.
+#ifndef B200_ONE_TOKEN_DEFAULT
+#define B200_ONE_TOKEN_DEFAULT 2
+#endif
+int one_token_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("B200_ONE_TOKEN");
+    const int v = e != nullptr ? atoi(e) : B200_ONE_TOKEN_DEFAULT;
+    mode = (v >= 0 && v <= 2) ? v : B200_ONE_TOKEN_DEFAULT;
   }
   return mode;
 }
@@ -145,7 +169,7 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
                            int64_t M, int64_t D, int64_t H, int cf, int kernel, void* stream) {
   const char* fn = "b200_twell_pack";
   B200_TRY(check_dims(fn, M, D, H, cf));
-  if (kernel < 0 || kernel > 5) return fail(B200_EINVAL, "%s: kernel must be 0..5", fn);
+  if (kernel < 0 || kernel > 6) return fail(B200_EINVAL, "%s: kernel must be 0..6", fn);
   if (M == 0) return B200_OK;
   B200_TRY(check_ptr(fn, "x", x));
   B200_TRY(check_ptr(fn, "w", w));
@@ -162,6 +186,11 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
   // A d_ff shard of at most 8 tiles (2048 neurons) fills too few SMs with a 4-way split:
   // the 8-way split takes 8.5 us against 11.0 us there, but loses from 16 tiles on
   // (15.9 against 11.2 us at 4096 neurons), where its 8-CTA clusters no longer fit one wave.
+  // One token: a warp reduces a whole weight row by itself (no split-k exchange).
+  if (kernel == 6 || (kernel == 0 && one_token_mode() >= 1 && twell_gemv_serves(M, D, H))) {
+    if (M != 1) return fail(B200_EUNSUPPORTED, "%s: kernel 6 serves one token", fn);
+    return twell_gemv_pack(x, w, bias, packed, D, H, cf, st);
+  }
   if (kernel == 0 && M > 16 && M <= 32 && H <= 8 * kTileN && D % 512 == 0)
     return twell_pack_tc_splitk8(x, w, bias, packed, M, D, H, cf, st);
   if (kernel == 3 || (kernel == 0 && M > 16 && M <= 32))
@@ -250,6 +279,12 @@ bool decode_wanted(int64_t M, int64_t D, int64_t H, const void* workspace,
   return need > 0 && workspace_bytes >= need;
 }
 
+bool one_token_wanted(int64_t M, int64_t D, int64_t H, const void* workspace,
+                      size_t workspace_bytes) {
+  return one_token_mode() == 2 && workspace != nullptr && twell_gemv_serves(M, D, H) &&
+         workspace_bytes >= twell_gemv_workspace_bytes(D, H);
+}
+
 int decode_dispatch(bool gated, bool hp, const void* x, const void* gate, const float* bias,
                     const void* up, const void* down, void* packed, void* out, int64_t M,
                     int64_t D, int64_t H, int cf, void* workspace, size_t workspace_bytes,
@@ -325,6 +360,14 @@ int b200_twell_gated_mlp(const void* x, const void* gate, const float* gate_bias
     const int rc = decode_dispatch(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, gate,
                                    gate_bias, up, down, packed, out, M, D, H, cf, workspace,
                                    workspace_bytes, nullptr, 0, static_cast<cudaStream_t>(stream));
+    if (rc != B200_EUNSUPPORTED) return rc;  // served (or failed for good)
+  }
+  if (one_token_wanted(M, D, H, workspace, workspace_bytes)) {
+    B200_TRY(check_decode_args("b200_twell_gated_mlp", x, gate, gate_bias, up, down, packed, out,
+                               M, D, H, cf, flags, workspace, true));
+    const int rc = twell_gemv_layer(true, (flags & B200_FLAG_HIGH_PRECISION) != 0, x, gate,
+                                    gate_bias, up, down, packed, out, D, H, cf, workspace,
+                                    workspace_bytes, static_cast<cudaStream_t>(stream));
     if (rc != B200_EUNSUPPORTED) return rc;  // served (or failed for good)
   }
   B200_TRY(b200_twell_pack(x, gate, gate_bias, packed, M, D, H, cf, stream));
@@ -406,6 +449,15 @@ int b200_twell_mlp(const void* x, const void* up, const void* down, void* packed
     const int rc = decode_dispatch(false, false, x, up, nullptr, nullptr, down, packed, out, M, D,
                                    H, cf, workspace, workspace_bytes, nullptr, 0,
                                    static_cast<cudaStream_t>(stream));
+    if (rc != B200_EUNSUPPORTED) return rc;
+  }
+  if ((num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8) &&
+      one_token_wanted(M, D, H, workspace, workspace_bytes)) {
+    B200_TRY(check_decode_args("b200_twell_mlp", x, up, nullptr, nullptr, down, packed, out, M, D,
+                               H, cf, 0, workspace, false));
+    const int rc = twell_gemv_layer(false, false, x, up, nullptr, nullptr, down, packed, out, D,
+                                    H, cf, workspace, workspace_bytes,
+                                    static_cast<cudaStream_t>(stream));
     if (rc != B200_EUNSUPPORTED) return rc;
   }
   B200_TRY(b200_twell_pack(x, up, nullptr, packed, M, D, H, cf, stream));

@@ -100,7 +100,35 @@ def run_batch(b: int, d: int, h: int, layers, dev) -> dict:
                   0, big.data_ptr(), big.numel(), nxt.data_ptr() if prefetch else None,
                   wbytes if prefetch else 0)
 
+    def pack_mma(l):
+        _lib.call("b200_twell_pack_select", dev, x.data_ptr(), layers[l][0].data_ptr(), None,
+                  packed.data_ptr(), b, d, h, 8, 1)
+
+    def two_mma(l):
+        g, u, dn = layers[l]
+        pack_mma(l)
+        _lib.call("b200_twell_gated_t2d", dev, x.data_ptr(), packed.data_ptr(), u.data_ptr(),
+                  dn.data_ptr(), y[l].data_ptr(), b, d, h, 8, 0, small.data_ptr(), small.numel())
+
+    def layer_call(l):
+        g, u, dn = layers[l]
+        _lib.call("b200_twell_gated_mlp", dev, x.data_ptr(), g.data_ptr(), None, u.data_ptr(),
+                  dn.data_ptr(), packed2.data_ptr(), y2[l].data_ptr(), b, d, h, 8, 0,
+                  one_ws.data_ptr(), one_ws.numel())
+
     rec = {"batch": b, "d_model": d, "d_ff": h, "layers": L}
+    if b == 1 and d in (2048, 4096):
+        # one token: GEMV pack kernel (automatic) against the mma.sync kernel, and the whole
+        # layer in the GEMV kernel (b200_twell_gated_mlp with a workspace for its partial rows)
+        one_ws = torch.zeros(4096 * 4 + (h // 256) * d * 4, dtype=torch.uint8, device=dev)
+        rec["pack_mma_sync_us"] = _graph_us(lambda: [pack_mma(l) for l in range(L)], L)
+        rec["two_kernels_mma_sync_pack_us"] = _graph_us(lambda: [two_mma(l) for l in range(L)], L)
+        rec["one_token_layer_us"] = _graph_us(lambda: [layer_call(l) for l in range(L)], L)
+        two(0)
+        layer_call(0)
+        torch.cuda.synchronize()
+        diff = y[0].float() - y2[0].float()
+        rec["one_token_rel_l2_vs_two_kernels"] = float(diff.norm() / y[0].float().norm())
     rec["two_kernels_us"] = _graph_us(lambda: [two(l) for l in range(L)], L)
     rec["two_kernels_with_l2_prefetch_us"] = _graph_us(
         lambda: [two_prefetch(l) for l in range(L)], L)
