@@ -69,18 +69,24 @@ int b200_twell_pack(const void* x, const void* w, const float* bias, void* packe
 
 /*
  * Same as b200_twell_pack with the kernel family chosen by the caller:
- *   kernel 0 = automatic (M == 1: kernel 6 where it serves; M <= 16: split-k cluster kernel on mma.sync; 17..32: tcgen05
+ *   kernel 0 = automatic (M == 1: kernel 6 where it serves; M <= 16: split-k cluster kernel on mma.sync;
+ *              33..256: kernel 8 / 9 while one wave; 17..32: tcgen05
  *              split-k cluster kernel; M > 32: tcgen05 / TMEM / TMA tile kernel),
  *   kernel 1 = mma.sync split-k cluster kernel (any M),
- *   kernel 2 = tcgen05 tile kernel (64 or 128 tokens per CTA tile; from 1024 tokens on,
- *              two co-resident 128-token CTAs per SM),
+ *   kernel 2 = tcgen05 tile kernel (64 tokens per CTA tile up to 64 tokens, kernel 7 above;
+ *              with B200_PACK_TILE=128: 128-token tiles, two co-resident CTAs per SM from
+ *              1024 tokens on),
  *   kernel 3 = tcgen05 split-k cluster kernel (32 tokens per tile, D split 4 ways),
  *   kernel 4 = tcgen05 tile kernel, two co-resident 128-token CTAs per SM at any M,
  *   kernel 5 = tcgen05 split-k cluster kernel with D split 8 ways (D % 512 == 0; chosen
  *              automatically for 17..32 tokens when H <= 2048, e.g. a narrow d_ff shard),
  *   kernel 6 = one-token GEMV kernel (M == 1, D 2048 or 4096): each warp reduces whole
  *              weight rows against the token held in registers, no split-k exchange; chosen
- *              automatically for such calls unless B200_ONE_TOKEN=0.
+ *              automatically for such calls unless B200_ONE_TOKEN=0,
+ *   kernel 7 = tcgen05 tile kernel with 256-token tiles, one CTA per SM and sixteen epilogue
+ *              warps (what kernels 0 and 2 run above 64 tokens unless B200_PACK_TILE=128),
+ *   kernel 8 / 9 = tcgen05 split-k cluster kernel with 128-token tiles, D split 4 / 2 ways
+ *              (chosen automatically for 33..256 tokens while its grid is a single wave).
  * All produce identical slab bytes on exact-arithmetic inputs.  No reference
  * counterpart (the reference has one WGMMA kernel, matmul_d2t.cu:287-709).
  */

@@ -34,6 +34,12 @@ int twell_pack_tc_pair(const void* x, const void* w, const float* bias, void* pa
                        int64_t D, int64_t H, int cf, cudaStream_t stream);
 int twell_pack_tc_splitk8(const void* x, const void* w, const float* bias, void* packed,
                           int64_t M, int64_t D, int64_t H, int cf, cudaStream_t stream);
+int twell_pack_tc_splitk_mid(const void* x, const void* w, const float* bias, void* packed,
+                             int64_t M, int64_t D, int64_t H, int cf, int split,
+                             cudaStream_t stream);
+int twell_pack_mid_split(int64_t M, int64_t H, int sm_count);
+int twell_pack_tc_wide(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                       int64_t D, int64_t H, int cf, cudaStream_t stream);
 int twell_pack_tc_status();
 int twell_t2d_launch(bool gated, bool hp, const void* x, const void* packed, const void* up,
                      const void* down, void* out, int64_t M, int64_t D, int64_t H, int cf,
@@ -169,7 +175,7 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
                            int64_t M, int64_t D, int64_t H, int cf, int kernel, void* stream) {
   const char* fn = "b200_twell_pack";
   B200_TRY(check_dims(fn, M, D, H, cf));
-  if (kernel < 0 || kernel > 6) return fail(B200_EINVAL, "%s: kernel must be 0..6", fn);
+  if (kernel < 0 || kernel > 9) return fail(B200_EINVAL, "%s: kernel must be 0..9", fn);
   if (M == 0) return B200_OK;
   B200_TRY(check_ptr(fn, "x", x));
   B200_TRY(check_ptr(fn, "w", w));
@@ -197,6 +203,14 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
     return twell_pack_tc_splitk(x, w, bias, packed, M, D, H, cf, st);
   if (kernel == 4) return twell_pack_tc_pair(x, w, bias, packed, M, D, H, cf, st);
   if (kernel == 5) return twell_pack_tc_splitk8(x, w, bias, packed, M, D, H, cf, st);
+  if (kernel == 7) return twell_pack_tc_wide(x, w, bias, packed, M, D, H, cf, st);
+  if (kernel == 8) return twell_pack_tc_splitk_mid(x, w, bias, packed, M, D, H, cf, 4, st);
+  if (kernel == 9) return twell_pack_tc_splitk_mid(x, w, bias, packed, M, D, H, cf, 2, st);
+  // 33..256 tokens: 128-token tiles with d_model split over a cluster while that grid is one wave.
+  if (kernel == 0 && M > 32 && M <= 256) {
+    const int split = twell_pack_mid_split(M, H, sm_count());
+    if (split != 0) return twell_pack_tc_splitk_mid(x, w, bias, packed, M, D, H, cf, split, st);
+  }
   const bool use_tc = kernel == 2 || (kernel == 0 && M > 32);
   return use_tc ? twell_pack_tc(x, w, bias, packed, M, D, H, cf, st)
                 : twell_pack_small(x, w, bias, packed, M, D, H, cf, st);

@@ -303,6 +303,161 @@ dense_rows_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
   }
 }
 
+// The same GEMM as ONE CTA per SM on 256-token tiles with sixteen epilogue warps: the two
+// accumulators fill all 512 TMEM columns, a 64-k stage is 32 KB of A rows + 32 KB of token rows
+// (131 flop per staged byte against 87 for the 128-token tile, which is what the L2 -> SM
+// operand stream limits), and the epilogue is spread over four groups of four warps that take
+// every fourth 32-token block.  Used when the host knows the row count and the grid fills the GPU.
+constexpr int kThreadsDenseWide = 64 + 512;
+
+template <int STAGES, bool DUAL>
+__global__ void __launch_bounds__(kThreadsDenseWide, 1)
+dense_rows_gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a0,
+                            const __grid_constant__ CUtensorMap tmap_a1,
+                            const __grid_constant__ CUtensorMap tmap_b,
+                            const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                            const int* __restrict__ row_ids, int n_rows, int K, int ld_out,
+                            int group) {
+  constexpr int NTOK = 256;
+  constexpr int kBTileBytes = NTOK * 128;
+  constexpr int kStageBytes = 2 * kATileBytes + kBTileBytes;
+  constexpr uint32_t kTmemCols = 2 * NTOK;
+  constexpr uint32_t kIdesc = umma_idesc(128, NTOK);
+
+  int tile, mblk;
+  raster_remap(group, tile, mblk);
+  const int m0 = mblk * NTOK;
+  if (m0 >= n_rows) return;  // uniform for the CTA: nothing allocated yet
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ksteps = K / kStageK;
+  const int a0_row = DUAL ? tile * 128 : tile * 256;
+  const int a1_row = DUAL ? tile * 128 : tile * 256 + 128;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+          abort_s = 1;
+          atomicExch(&g_dense_error, 1);
+          break;
+        }
+        unsigned char* st = smem + (size_t)s * kStageBytes;
+        mbar_expect_tx(&full_bar[s], (uint32_t)kStageBytes);
+        tma_load_2d(st, &tmap_a0, k * kStageK, a0_row, &full_bar[s]);
+        tma_load_2d(st + kATileBytes, DUAL ? &tmap_a1 : &tmap_a0, k * kStageK, a1_row,
+                    &full_bar[s]);
+        tma_load_2d(st + 2 * kATileBytes, &tmap_b, k * kStageK, m0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], phase)) {
+          abort_s = 1;
+          atomicExch(&g_dense_error, 2);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(smem + (size_t)s * kStageBytes);
+        const uint64_t da0 = umma_desc(a0), da1 = umma_desc(a0 + kATileBytes),
+                       db = umma_desc(a0 + 2 * kATileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kStageK / 16; ++kk) {
+          const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, da0 + 2 * kk, db + 2 * kk, kIdesc, acc);
+          umma_bf16(tmem_base + NTOK, da1 + 2 * kk, db + 2 * kk, kIdesc, acc);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (!abort_s) umma_commit(&acc_bar);
+    }
+  } else {
+    // ---- epilogue: group g = (warp - 2) / 4 takes token blocks g, g + 4; quarter = warp % 4 ----
+    const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;
+    bool ok = mbar_wait(&acc_bar, 0u);
+    if (!ok) {
+      abort_s = 1;
+      atomicExch(&g_dense_error, 3);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const int f0 = a0_row + q * 32 + lane;  // output feature of accumulator 0
+    const float b0 = (DUAL && bias != nullptr) ? bias[f0] : 0.f;
+    for (int tb = grp; tb < NTOK / 32 && ok; tb += 4) {
+      if (m0 + tb * 32 >= n_rows) break;
+      float v0[32], v1[32];
+      tmem_ld32(lane_addr + (uint32_t)(tb * 32), v0);
+      tmem_ld32(lane_addr + (uint32_t)(NTOK + tb * 32), v1);
+      if (DUAL) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int tok = m0 + tb * 32 + c;
+          if (tok >= n_rows) break;
+          const float g = v0[c] + b0;
+          float h = 0.f;
+          if (g > 0.f)
+            h = __bfloat162float(__float2bfloat16_rn(g)) * __bfloat162float(__float2bfloat16_rn(v1[c]));
+          out[(size_t)tok * ld_out + f0] = __float2bfloat16_rn(h);
+        }
+      } else {
+        const int t_mine = m0 + tb * 32 + lane;
+        const int rid = t_mine < n_rows ? (row_ids != nullptr ? row_ids[t_mine] : t_mine) : -1;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int r = __shfl_sync(0xffffffffu, rid, c);
+          if (r < 0) continue;
+          __nv_bfloat16* orow = out + (size_t)r * ld_out;
+          orow[f0] = __float2bfloat16_rn(v0[c]);
+          orow[f0 + 128] = __float2bfloat16_rn(v1[c]);
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -592,6 +747,29 @@ int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void
     if (int rc = make_map(&map_a0, a0, a_rows, K, 128, KS)) return rc;
     if (int rc = make_map(&map_a1, a1, a_rows, K, 128, KS)) return rc;
     if (int rc = make_map(&map_b, b, b_rows, K, kDenseTok, KS)) return rc;
+  }
+  // Host-known row count and enough 256-token tiles to fill the GPU: one CTA per SM on
+  // 256-token tiles with sixteen epilogue warps (B200_DENSE_WIDE=0 keeps the 128-token tiles).
+  static const bool wide_on = [] {
+    const char* e = getenv("B200_DENSE_WIDE");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  const int64_t wide_ctas = (int64_t)feature_tiles * ((cap + 255) / 256);
+  if (KS == 64 && wide_on && n_rows_ptr == nullptr && wide_ctas * 5 >= (int64_t)sm_count() * 4) {
+    CUtensorMap map_b256;
+    if (int rc = make_map(&map_b256, b, b_rows, K, 256)) return rc;
+    constexpr int WST = 3;
+    const size_t smem_w = (size_t)WST * (2 * kATileBytes + 256 * 128) + 1024;
+    auto wide = dense_rows_gemm_wide_kernel<WST, DUAL>;
+    static size_t granted_w[64] = {0};
+    if (int rc = ensure_dynamic_smem(wide, smem_w, granted_w, "b200_twell_gated_t2d_hybrid"))
+      return rc;
+    dim3 wgrid((unsigned)feature_tiles, (unsigned)((cap + 255) / 256), 1);
+    wide<<<wgrid, kThreadsDenseWide, smem_w, stream>>>(
+        map_a0, map_a1, map_b256, bias, static_cast<__nv_bfloat16*>(out), row_ids, (int)cap,
+        (int)K, (int)ld_out,
+        raster_group((DUAL ? 2 : 1) * a_rows * K * 2, (int64_t)256 * K * 2));
+    return check_launch("b200_twell_gated_t2d_hybrid (dense rows, 256-token tiles)");
   }
   dim3 grid((unsigned)(a_rows / (DUAL ? 128 : 256)), (unsigned)((cap + kDenseTok - 1) / kDenseTok), 1);
   // A grid of at most one CTA per SM (the weight-gradient products at d_model 1024: 128

@@ -153,6 +153,23 @@ __device__ __forceinline__ bool epi_barrier_and(bool v) {
   return r != 0;
 }
 
+// Named barrier `id` (1..15) for `count` threads (a multiple of 32).
+__device__ __forceinline__ void named_barrier(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// Barrier `id` over `count` threads that also ANDs a flag over them.
+__device__ __forceinline__ bool named_barrier_and(int id, int count, bool v) {
+  uint32_t r;
+  asm volatile(
+      "{\n.reg .pred p, q;\nsetp.ne.u32 q, %3, 0;\n"
+      "bar.red.and.pred p, %1, %2, q;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(r)
+      : "r"(id), "r"(count), "r"((uint32_t)v)
+      : "memory");
+  return r != 0;
+}
+
 // Launch order of a (feature tiles, token blocks) grid.  CTAs start in the order of their linear
 // index; walking that index down `group` token blocks before moving on to the next feature
 // tile keeps the token rows of one group in L2 while the weight matrix streams past once per

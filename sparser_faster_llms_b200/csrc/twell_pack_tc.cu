@@ -399,6 +399,189 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
 }
 
 // ---------------------------------------------------------------------------
+// Large-M kernel with sixteen epilogue warps: ONE CTA per SM computes 256 neurons x 256 tokens
+// (two 128-lane accumulators of 256 columns = all of TMEM; a stage of 64 k-values is 32 KB of
+// weights + 32 KB of tokens, i.e. 131 flop per staged byte against 87 for the 128-token tile),
+// and the pack epilogue - which four warps need about 2 us per 32-token block for - is spread
+// over four groups of four warps that each take every fourth token block.  The epilogue
+// reads the accumulators twice (signs first, values again when the slots are known) so that a
+// thread holds 32 instead of 64 of them.
+// Threads: warp 0 producer, warp 1 mma, warps 2..17 epilogue (group = (warp - 2) / 4, TMEM
+// lane quarter = warp % 4).  grid = (H / 256, ceil(M / 256)).
+// ---------------------------------------------------------------------------
+constexpr int kThreadsTcWideM = 64 + 512;
+
+template <int STAGES>
+__global__ void __launch_bounds__(kThreadsTcWideM, 1)
+twell_pack_tc_wide_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                          const __grid_constant__ CUtensorMap tmap_x,
+                          const float* __restrict__ bias, uint32_t* __restrict__ packed, int M,
+                          int D, int slab_w, int row_words, int group) {
+  constexpr int NTOK = 256;
+  constexpr int kBTileBytes = NTOK * 128;
+  constexpr int kStageBytes = 2 * kATileBytes + kBTileBytes;
+  constexpr uint32_t kTmemCols = 2 * NTOK;
+  constexpr uint32_t kIdesc = umma_idesc(128, NTOK);
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_s;
+  __shared__ uint32_t masks_s[4][32][8];
+  __shared__ int prefix_s[4][32][8];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int tile, mblk;
+  raster_remap(group, tile, mblk);
+  const int m0 = mblk * NTOK;
+  const int ksteps = D / kStageK;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+          abort_s = 1;
+          atomicExch(&g_tc_error, 1);
+          break;
+        }
+        unsigned char* st = smem + (size_t)s * kStageBytes;
+        mbar_expect_tx(&full_bar[s], (uint32_t)kStageBytes);
+        tma_load_2d(st, &tmap_w, k * kStageK, tile * kTileN, &full_bar[s]);  // 256 rows: A0 | A1
+        tma_load_2d(st + 2 * kATileBytes, &tmap_x, k * kStageK, m0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], phase)) {
+          abort_s = 1;
+          atomicExch(&g_tc_error, 2);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(smem + (size_t)s * kStageBytes);
+        const uint64_t da0 = umma_desc(a0), da1 = umma_desc(a0 + kATileBytes),
+                       db = umma_desc(a0 + 2 * kATileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kStageK / 16; ++kk) {
+          const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, da0 + 2 * kk, db + 2 * kk, kIdesc, acc);
+          umma_bf16(tmem_base + NTOK, da1 + 2 * kk, db + 2 * kk, kIdesc, acc);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (!abort_s) umma_commit(&acc_bar);
+    }
+  } else {
+    const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;              // 0..3
+    const int gt = (int)threadIdx.x - 64 - grp * 128;  // 0..127 inside the group
+    const int bar_id = 2 + grp;
+    bool ok = mbar_wait(&acc_bar, 0u);
+    if (!ok) {
+      abort_s = 1;
+      atomicExch(&g_tc_error, 3);
+    }
+    ok = named_barrier_and(1, 512, ok);  // the same decision in all 512 epilogue threads
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int n_lo = tile * kTileN + q * 32 + lane;  // neuron of accumulator 0; +128 for 1
+    const float b_lo = bias != nullptr ? bias[n_lo] : 0.f;
+    const float b_hi = bias != nullptr ? bias[n_lo + 128] : 0.f;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint32_t (*masks)[8] = masks_s[grp];
+    int (*prefix)[8] = prefix_s[grp];
+    for (int tb = grp; tb < NTOK / 32 && ok; tb += 4) {
+      if (m0 + tb * 32 >= M) break;  // the same in every thread of the group
+      float v[32];
+      // signs
+      tmem_ld32(lane_addr + (uint32_t)(tb * 32), v);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const uint32_t k = __ballot_sync(0xffffffffu, m0 + tb * 32 + c < M && v[c] + b_lo > 0.f);
+        if (lane == 0) masks[c][q] = k;
+      }
+      tmem_ld32(lane_addr + (uint32_t)(NTOK + tb * 32), v);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const uint32_t k = __ballot_sync(0xffffffffu, m0 + tb * 32 + c < M && v[c] + b_hi > 0.f);
+        if (lane == 0) masks[c][4 + q] = k;
+      }
+      named_barrier(bar_id, 128);
+      if (gt < 32) {
+        const int tok = m0 + tb * 32 + gt;
+        int run = 0;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          prefix[gt][ch] = run;
+          run += __popc(masks[gt][ch]);
+        }
+        if (tok < M) packed[(size_t)tok * row_words + (size_t)tile * slab_w] = (uint32_t)run;
+      }
+      named_barrier(bar_id, 128);
+      // values (accumulator 1 is still in v; accumulator 0 is read again)
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const uint32_t k = masks[c][4 + q];
+        if ((k >> lane) & 1u) {
+          const int slot = prefix[c][4 + q] + __popc(k & lanemask_lt());
+          if (slot < slab_w - 1)
+            packed[(size_t)(m0 + tb * 32 + c) * row_words + (size_t)tile * slab_w + 1 + slot] =
+                (uint32_t)(n_lo + 128) | (bf16_bits(v[c] + b_hi) << 16);
+        }
+      }
+      tmem_ld32(lane_addr + (uint32_t)(tb * 32), v);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const uint32_t k = masks[c][q];
+        if ((k >> lane) & 1u) {
+          const int slot = prefix[c][q] + __popc(k & lanemask_lt());
+          if (slot < slab_w - 1)
+            packed[(size_t)(m0 + tb * 32 + c) * row_words + (size_t)tile * slab_w + 1 + slot] =
+                (uint32_t)n_lo | (bf16_bits(v[c] + b_lo) << 16);
+        }
+      }
+      named_barrier(bar_id, 128);  // masks / prefix are rewritten by the group's next block
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
 // The same split-k kernel with sixteen epilogue warps instead of four.  The epilogue of the
 // four-warp form is a latency chain on one warp per scheduler (TMEM read, 64 remote stores
 // per thread, then 16 elements per thread to sum, ballot and store).  Here four groups of
@@ -595,6 +778,205 @@ twell_pack_tc_splitk_wide_kernel(const __grid_constant__ CUtensorMap tmap_w,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Split-k kernel for 33..256 tokens: the decode kernel above with 128-token tiles.  A tile of
+// 256 neurons x 128 tokens has only H / 256 CTAs to itself when d_model is not split (32 at
+// d_ff 8192: 32 SMs walking 32 latency-bound k-steps, 31-36 us per call whatever the token
+// count); split four ways over a cluster every SM streams a quarter of the weight rows.
+// The fp32 partial tile of a CTA (128 KB) does not fit next to the operand ring, so the
+// partial sums land in the ring itself: a cluster barrier after every CTA's last MMA (instead
+// of the early arrive of the decode kernel) makes the ring free, then the TMEM -> DSMEM push,
+// a second cluster barrier and the same final pass (CTA r owns 128 / CL tokens).
+// grid = ((H/256) * CL, ceil(M / 128)), cluster = CL (4, or 2 when four CTAs per tile would not
+// fit one wave), 576 threads.
+// ---------------------------------------------------------------------------
+constexpr int kTokMid = 128;
+
+template <int CL, int STAGES>
+__global__ void __launch_bounds__(kThreadsTcWide, 1)
+twell_pack_tc_splitk_mid_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                                const __grid_constant__ CUtensorMap tmap_x,
+                                const float* __restrict__ bias, uint32_t* __restrict__ packed,
+                                int M, int D, int slab_w, int row_words) {
+  constexpr int NTOK = kTokMid;
+  constexpr int TOK = NTOK / CL;  // tokens finalised per CTA: 32 (CL 4) or 64 (CL 2)
+  static_assert(CL == 2 || CL == 4, "cluster size");
+  constexpr int kBTileBytes = NTOK * 128;
+  constexpr int kStageBytes = 2 * kATileBytes + kBTileBytes;
+  constexpr uint32_t kTmemCols = 2 * NTOK;
+  constexpr uint32_t kIdesc = umma_idesc(128, NTOK);
+  constexpr int EPT = TOK * kTileN / 512;  // elements per epilogue thread in the final pass
+  static_assert((size_t)NTOK * kPartStrideTc * sizeof(float) <= (size_t)STAGES * kStageBytes,
+                "the partial sums must fit into the operand ring");
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* part = reinterpret_cast<float*>(smem);  // [CL source ranks x TOK][kPartStrideTc], after the ring is free
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_s;
+  __shared__ int cnt_chunk[TOK][8];
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int crank = (int)cluster.block_rank();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / CL;
+  const int m0 = blockIdx.y * NTOK;
+  const int kc = D / CL;
+  const int ksteps = kc / kStageK;
+  const int k_base = crank * kc;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_slot;
+  pdl_wait();
+
+  bool ok = true;
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+          abort_s = 1;
+          atomicExch(&g_tc_error, 1);
+          break;
+        }
+        unsigned char* st = smem + (size_t)s * kStageBytes;
+        mbar_expect_tx(&full_bar[s], (uint32_t)kStageBytes);
+        const int kcoord = k_base + k * kStageK;
+        tma_load_2d(st, &tmap_w, kcoord, tile * kTileN, &full_bar[s]);  // 256 rows: A0 | A1
+        tma_load_2d(st + 2 * kATileBytes, &tmap_x, kcoord, m0, &full_bar[s]);
+      }
+      pdl_launch_dependents();
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], phase)) {
+          abort_s = 1;
+          atomicExch(&g_tc_error, 2);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(smem + (size_t)s * kStageBytes);
+        const uint64_t da0 = umma_desc(a0), da1 = umma_desc(a0 + kATileBytes),
+                       db = umma_desc(a0 + 2 * kATileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kStageK / 16; ++kk) {
+          const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, da0 + 2 * kk, db + 2 * kk, kIdesc, acc);
+          umma_bf16(tmem_base + NTOK, da1 + 2 * kk, db + 2 * kk, kIdesc, acc);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (!abort_s) umma_commit(&acc_bar);
+    }
+  } else {
+    // every MMA of this CTA has read its operands once the accumulators are published
+    ok = mbar_wait(&acc_bar, 0u);
+    if (!ok) {
+      abort_s = 1;
+      atomicExch(&g_tc_error, 3);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+  // Every CTA of the cluster is past its last MMA (or has given up): the rings are free.
+  cluster.sync();
+
+  if (warp >= 2 && ok) {
+    // ---- epilogue part 1: TMEM -> registers -> the owner's ring memory ----
+    const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;  // token columns [32 grp, 32 grp + 32)
+    const int owner = grp * 32 / TOK, tl0 = grp * 32 % TOK;
+    const int nl = q * 32 + lane;     // neuron inside the tile (accumulator 0); +128 for 1
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(grp * 32);
+    float* dst0 = cluster.map_shared_rank(part, owner) +
+                  (size_t)(crank * TOK + tl0) * kPartStrideTc + nl;
+    float v[32];
+    tmem_ld32(lane_addr, v);
+#pragma unroll
+    for (int c = 0; c < 32; ++c) dst0[(size_t)c * kPartStrideTc] = v[c];
+    tmem_ld32(lane_addr + (uint32_t)NTOK, v);
+#pragma unroll
+    for (int c = 0; c < 32; ++c) dst0[(size_t)c * kPartStrideTc + 128] = v[c];
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  cluster.sync();  // all partials delivered (every thread of every CTA takes part)
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+  if (warp < 2 || abort_s) return;
+
+  // ---- epilogue part 2: this CTA finalises tokens [crank*TOK, (crank+1)*TOK) ----
+  const int et = threadIdx.x - 64;  // 0..511
+  const int neuron0 = tile * kTileN;
+  float z[EPT];
+  uint32_t mask[EPT];
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int e = et + i * 512;
+    const int tl = e / kTileN, nl = e % kTileN;
+    const int tok = crank * TOK + tl;
+    float v = 0.f;
+#pragma unroll
+    for (int r = 0; r < CL; ++r) v += part[(size_t)(r * TOK + tl) * kPartStrideTc + nl];
+    if (bias != nullptr) v += bias[neuron0 + nl];
+    const bool keep = (v > 0.f) && (m0 + tok < M);
+    z[i] = v;
+    mask[i] = __ballot_sync(0xffffffffu, keep);
+    if (lane == 0) cnt_chunk[tl][nl / 32] = __popc(mask[i]);
+  }
+  named_barrier2(512);
+  if (et < TOK) {  // counts -> exclusive prefix over the 8 chunks of this token, count word
+    int run = 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int v = cnt_chunk[et][c];
+      cnt_chunk[et][c] = run;
+      run += v;
+    }
+    const int tok = m0 + crank * TOK + et;
+    if (tok < M) packed[(size_t)tok * row_words + (size_t)tile * slab_w] = (uint32_t)run;
+  }
+  named_barrier2(512);
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int e = et + i * 512;
+    const int tl = e / kTileN, nl = e % kTileN;
+    const int tok = crank * TOK + tl;
+    if (m0 + tok >= M) continue;
+    uint32_t* slab = packed + (size_t)(m0 + tok) * row_words + (size_t)tile * slab_w;
+    const int slot = cnt_chunk[tl][nl / 32] + __popc(mask[i] & lanemask_lt());
+    if (((mask[i] >> lane) & 1u) && slot < slab_w - 1)
+      slab[1 + slot] = (uint32_t)(neuron0 + nl) | (bf16_bits(z[i]) << 16);
+  }
+}
+
 // ---- host side -------------------------------------------------------------
 template <int NTOK, int STAGES, int MINB = 1>
 int launch_tc(const void* x, const void* w, const float* bias, void* packed, int64_t M, int64_t D,
@@ -613,6 +995,59 @@ int launch_tc(const void* x, const void* w, const float* bias, void* packed, int
                                            (int)M, (int)D, slab_w, tiles * slab_w,
                                            raster_group(H * D * 2, (int64_t)NTOK * D * 2));
   return check_launch("b200_twell_pack (tcgen05)");
+}
+
+template <int STAGES>
+int launch_tc_wide(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                   int64_t D, int64_t H, int cf, cudaStream_t stream) {
+  CUtensorMap map_w, map_x;
+  if (int rc = make_map(&map_w, w, H, D, 256)) return rc;
+  if (int rc = make_map(&map_x, x, M, D, 256)) return rc;
+  const size_t smem = (size_t)STAGES * (2 * kATileBytes + 256 * 128) + 1024;
+  auto kern = twell_pack_tc_wide_kernel<STAGES>;
+  static size_t granted[64] = {0};
+  if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_pack")) return rc;
+  const int slab_w = kTileN / cf;
+  const int tiles = (int)(H / kTileN);
+  dim3 grid((unsigned)tiles, (unsigned)((M + 255) / 256), 1);
+  kern<<<grid, kThreadsTcWideM, smem, stream>>>(map_w, map_x, bias,
+                                                static_cast<uint32_t*>(packed), (int)M, (int)D,
+                                                slab_w, tiles * slab_w,
+                                                raster_group(H * D * 2, (int64_t)256 * D * 2));
+  return check_launch("b200_twell_pack (tcgen05, 256-token tiles)");
+}
+
+template <int CL, int STAGES>
+int launch_tc_splitk_mid(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                         int64_t D, int64_t H, int cf, cudaStream_t stream) {
+  CUtensorMap map_w, map_x;
+  if (int rc = make_map(&map_w, w, H, D, 256)) return rc;
+  if (int rc = make_map(&map_x, x, M, D, kTokMid)) return rc;
+  const size_t smem = (size_t)STAGES * (2 * kATileBytes + kTokMid * 128) + 1024;
+  auto kern = twell_pack_tc_splitk_mid_kernel<CL, STAGES>;
+  static size_t granted[64] = {0};
+  if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_pack")) return rc;
+  const int slab_w = kTileN / cf;
+  const int tiles = (int)(H / kTileN);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(tiles * CL), (unsigned)((M + kTokMid - 1) / kTokMid), 1);
+  cfg.blockDim = dim3(kThreadsTcWide, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = add_pdl_attribute(attr, 1, 1);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, bias,
+                                     static_cast<uint32_t*>(packed), (int)M, (int)D, slab_w,
+                                     tiles * slab_w);
+  if (e != cudaSuccess)
+    return fail(B200_ECUDA, "b200_twell_pack (tcgen05 split-k, 128-token tiles): launch: %s",
+                cudaGetErrorString(e));
+  return B200_OK;
 }
 
 // Epilogue form of the split-k kernel: sixteen epilogue warps unless B200_PACK_WIDE=0.
@@ -687,10 +1122,18 @@ int twell_pack_tc_splitk8(const void* x, const void* w, const float* bias, void*
 // Large-M path.  Needs D % 64 == 0 (guaranteed by D % 256 == 0).
 int twell_pack_tc(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                   int64_t D, int64_t H, int cf, cudaStream_t stream) {
-  // From 1024 tokens on, two co-resident 128-token CTAs per SM (each 256 TMEM columns and two
-  // 48 KB stages) hide one CTA's pack epilogue under the other's MMAs.  Measured on B200,
-  // M = 16384, D = 2048, H = 8192: 991 TFLOP/s, against 758 for one 256-token CTA with three
-  // stages (cuBLAS matmul + relu: 1270); equal at D = 4096; no gain at M = 512.
+  // Above 64 tokens: one CTA per SM on 256-token tiles with sixteen epilogue warps.  Measured
+  // on B200 against two co-resident 128-token CTAs per SM (four epilogue warps each) and
+  // cuBLAS matmul + relu, TFLOP/s at (M, D, H): (2048, 2048, 8192) 996 / 826 / 1063;
+  // (16384, 2048, 8192) 1222 / 995 / 1273; (16384, 2048, 11008) 1221 / 1002 / 1260;
+  // (2048, 4096, 16384) 1299 / 1102 / 1363; (16384, 4096, 16384) 1288 / 1222 / 1391;
+  // (16384, 1024, 4096) 855 / 681 / 994; at 100 tokens (D 2048, H 8192) 30.4 against 34.6 us
+  // for one 128-token tile per CTA.  B200_PACK_TILE=128 keeps the 128-token forms.
+  static const int tile_tokens = [] {
+    const char* e = getenv("B200_PACK_TILE");
+    return e != nullptr ? atoi(e) : 256;
+  }();
+  if (M > 64 && tile_tokens != 128) return launch_tc_wide<3>(x, w, bias, packed, M, D, H, cf, stream);
   if (M >= 1024) return launch_tc<128, 2, 2>(x, w, bias, packed, M, D, H, cf, stream);
   if (M > 64) return launch_tc<128, 4>(x, w, bias, packed, M, D, H, cf, stream);
   return launch_tc<64, 4>(x, w, bias, packed, M, D, H, cf, stream);
@@ -705,6 +1148,31 @@ int twell_pack_tc(const void* x, const void* w, const float* bias, void* packed,
 int twell_pack_tc_pair(const void* x, const void* w, const float* bias, void* packed, int64_t M,
                        int64_t D, int64_t H, int cf, cudaStream_t stream) {
   return launch_tc<128, 2, 2>(x, w, bias, packed, M, D, H, cf, stream);
+}
+
+// 33..256 tokens: split-k over a cluster of `split` (4 or 2) CTAs with 128-token tiles.
+int twell_pack_tc_splitk_mid(const void* x, const void* w, const float* bias, void* packed,
+                             int64_t M, int64_t D, int64_t H, int cf, int split,
+                             cudaStream_t stream) {
+  if (split == 2) return launch_tc_splitk_mid<2, 4>(x, w, bias, packed, M, D, H, cf, stream);
+  return launch_tc_splitk_mid<4, 4>(x, w, bias, packed, M, D, H, cf, stream);
+}
+
+// Cluster size for the 128-token split-k kernel: the largest of 4 and 2 whose grid is one
+// wave (one CTA per SM); 0 when neither is.  Measured on B200 (D 2048, d_ff 8192): 17.0 us
+// at 33..128 tokens against 27.4-29.5 us for unsplit tiles; at D 4096, d_ff 16384 and 128
+// tokens the four-way split needs two waves (45.6 against 50.2 us).
+int twell_pack_mid_split(int64_t M, int64_t H, int sm_count) {
+  const int64_t tiles = H / kTileN, blocks = (M + kTokMid - 1) / kTokMid;
+  if (tiles * 4 * blocks <= sm_count) return 4;
+  if (tiles * 2 * blocks <= sm_count) return 2;
+  return 0;
+}
+
+// One CTA per SM, 256 neurons x 256 tokens per tile, sixteen epilogue warps.
+int twell_pack_tc_wide(const void* x, const void* w, const float* bias, void* packed, int64_t M,
+                       int64_t D, int64_t H, int cf, cudaStream_t stream) {
+  return launch_tc_wide<3>(x, w, bias, packed, M, D, H, cf, stream);
 }
 
 // Error word raised by a bounded wait that gave up (0 = none).  Reads and clears it;

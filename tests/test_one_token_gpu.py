@@ -174,5 +174,5 @@ def test_refusals():
                                     256, 8, 6, None)
     assert rc == -4 and b"one token" in lib.b200_last_error()
     rc = lib.b200_twell_pack_select(x2.data_ptr(), w2.data_ptr(), None, p2.data_ptr(), 2, 2048,
-                                    256, 8, 7, None)
+                                    256, 8, 10, None)
     assert rc == -1

@@ -357,7 +357,12 @@ def test_tcgen05_pack_kernel_bit_exact_with_oracle_and_with_cluster_kernel(m, d,
     got_cl = to_np_u32(_pack_with(1, xg, gg, cf))
     got_sk = to_np_u32(_pack_with(3, xg, gg, cf))
     got_pair = to_np_u32(_pack_with(4, xg, gg, cf))  # two co-resident CTAs per SM
+    got_wide = to_np_u32(_pack_with(7, xg, gg, cf))  # 256-token tiles, sixteen epilogue warps
+    for k in (8, 9):                                 # 128-token tiles, d_model split 4 / 2 ways
+        assert np.array_equal(to_np_u32(_pack_with(k, xg, gg, cf)), want), k
+    assert np.array_equal(to_np_u32(_pack_with(0, xg, gg, cf)), want)   # what the library picks
     assert _lib.load_library().b200_twell_pack_tc_status() == 0
+    assert np.array_equal(got_wide, want)
     assert np.array_equal(got_tc, want)
     assert np.array_equal(got_cl, want)
     assert np.array_equal(got_sk, want)
