@@ -6,7 +6,7 @@
 
 // Built-in default of the programmatic-dependent-launch switch (B200_PDL overrides it).
 #ifndef B200_PDL_DEFAULT
-#define B200_PDL_DEFAULT 0
+#define B200_PDL_DEFAULT 3
 #endif
 
 namespace b200 {

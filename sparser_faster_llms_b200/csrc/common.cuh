@@ -57,16 +57,17 @@ inline int ensure_dynamic_smem(Kernel kern, size_t bytes, size_t (&granted)[64],
   return B200_OK;
 }
 
-// Programmatic dependent launch.  A kernel launched with the attribute below may become
-// resident while its predecessor in the stream still runs; it must execute pdl_wait() before
+// Programmatic dependent launch.  A kernel launched with the attribute below is set up by the
+// driver while its predecessor in the stream still runs; it must execute pdl_wait() before
 // its first global read of data the predecessor may write and before its first global write
 // (the wait returns once the predecessor grid has completed and its memory is visible).
-// pdl_launch_dependents() lets the successor's CTAs be scheduled as soon as every CTA of
-// this grid has started.  Both are no-ops in a kernel launched without the attribute.
+// No kernel here issues griddepcontrol.launch_dependents: with an explicit early trigger the
+// successor's CTAs become resident under the predecessor's tail and take shared memory and L1
+// from it (measured on B200, decode stack at batch 32: 0.79-0.83 ms per step against 0.70
+// without the attribute), whereas the implicit trigger at grid exit only removes the launch
+// latency between the two kernels (0.677 ms).  pdl_wait() is a no-op in a kernel launched
+// without the attribute.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-}
 
 // Whether the decode kernels are launched with programmatic stream serialisation
 // (environment variable B200_PDL: "0" switches it off, anything else or unset keeps the

@@ -148,8 +148,8 @@ twell_gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       for (int it = 0; it < DI; ++it)
         b[r][it] = ldg_stream(wrow + (size_t)(row0 + r) * (D / 8) + it * 32);
   };
-  request(buf[0], 0);  // weights do not depend on the predecessor in the stream
-  pdl_wait();
+  pdl_wait();  // before any global read: the predecessor may have written the weights too
+  request(buf[0], 0);
   uint4 xv[DI];
 #pragma unroll
   for (int it = 0; it < DI; ++it)

@@ -165,10 +165,6 @@ twell_pack_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     }
   }
 
-  // The weight stream of this CTA is consumed: the next kernel's CTAs may take their places
-  // and wait, under this kernel's reduction and compaction.
-  pdl_launch_dependents();
-
   // Push the partial pre-activations to the CTA that finalises each token:
   // owner r receives rank q's values in part[(q*TOK + local token)][neuron].
   cluster.barrier_wait();  // every CTA of the cluster is running (arrived at kernel start)

@@ -288,9 +288,6 @@ twell_pack_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w,
         tma_load_2d(st, &tmap_w, kcoord, tile * kTileN, &full_bar[s]);
         tma_load_2d(st + 2 * kATileBytes, &tmap_x, kcoord, m0, &full_bar[s]);
       }
-      // Every load of this CTA is in flight: the contraction's CTAs may now take their
-      // places and wait, under this kernel's epilogue.
-      pdl_launch_dependents();
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -669,7 +666,6 @@ twell_pack_tc_splitk_wide_kernel(const __grid_constant__ CUtensorMap tmap_w,
         tma_load_2d(st, &tmap_w, kcoord, tile * kTileN, &full_bar[s]);
         tma_load_2d(st + 2 * kATileBytes, &tmap_x, kcoord, m0, &full_bar[s]);
       }
-      pdl_launch_dependents();
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -868,7 +864,6 @@ twell_pack_tc_splitk_mid_kernel(const __grid_constant__ CUtensorMap tmap_w,
         tma_load_2d(st, &tmap_w, kcoord, tile * kTileN, &full_bar[s]);  // 256 rows: A0 | A1
         tma_load_2d(st + 2 * kATileBytes, &tmap_x, kcoord, m0, &full_bar[s]);
       }
-      pdl_launch_dependents();
     }
   } else if (warp == 1) {
     if (lane == 0) {
