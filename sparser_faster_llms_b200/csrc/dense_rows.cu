@@ -21,7 +21,11 @@
 // count exceeds the ELL width go to `tail_dense` and are multiplied with torch::matmul);
 // the TwELL inference kernels themselves have no such route
 // (custom_models/twell_modules/matmul_gated_t2d.cu:17-169 drops overflowed entries).
+#include <cooperative_groups.h>
+
 #include "tc_common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace b200 {
 
@@ -458,6 +462,183 @@ dense_rows_gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a0,
   }
 }
 
+// Split-k form of the same GEMM for at most a few hundred rows, where a (feature tile, token
+// block) grid is a handful of CTAs that each walk a long, latency-bound k-loop (the down
+// projection of 128 rows at D 2048 is 8 tiles of K = d_ff).  A cluster of CL CTAs owns a tile of
+// 128 features (DUAL: 128 gate + 128 up rows, two accumulators) x 128 rows and splits K; the
+// fp32 partial tiles are pushed into the operand rings once every CTA of the cluster is past its
+// last MMA (cluster barrier), CTA r then finalises rows [r * 128 / CL, (r + 1) * 128 / CL).
+// 576 threads: warp 0 producer, warp 1 mma, warps 2..17 epilogue (four groups of 32 rows).
+// grid = (a_rows / 128 * CL, ceil(rows / 128)), cluster = CL.
+template <int CL, int STAGES, bool DUAL>
+__global__ void __launch_bounds__(kThreadsDenseWide, 1)
+dense_rows_gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a0,
+                              const __grid_constant__ CUtensorMap tmap_a1,
+                              const __grid_constant__ CUtensorMap tmap_b,
+                              const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                              const int* __restrict__ row_ids, int n_rows, int K, int ld_out) {
+  constexpr int NTOK = 128;
+  constexpr int NACC = DUAL ? 2 : 1;
+  constexpr int TOK = NTOK / CL;  // rows finalised per CTA
+  constexpr int kBTileBytes = NTOK * 128;
+  constexpr int kStageBytes = NACC * kATileBytes + kBTileBytes;
+  constexpr uint32_t kTmemCols = NACC * NTOK;
+  constexpr uint32_t kIdesc = umma_idesc(128, NTOK);
+  constexpr int kStride = NACC * 128 + 4;    // floats per (source rank, row) of the exchange
+  constexpr int EPT = TOK * 128 / 512;       // outputs per epilogue thread in the final pass
+  static_assert(CL == 2 || CL == 4 || CL == 8, "cluster size");
+  static_assert((size_t)NTOK * kStride * sizeof(float) <= (size_t)STAGES * kStageBytes,
+                "the partial sums must fit into the operand ring");
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  float* part = reinterpret_cast<float*>(smem);  // [CL x TOK][kStride], once the ring is free
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int abort_s;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int crank = (int)cluster.block_rank();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / CL;
+  const int m0 = blockIdx.y * NTOK;
+  const int kc = K / CL;
+  const int ksteps = kc / kStageK;
+  const int k_base = crank * kc;
+  const int a_row = tile * 128;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_slot;
+
+  bool ok = true;
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+          abort_s = 1;
+          atomicExch(&g_dense_error, 1);
+          break;
+        }
+        unsigned char* st = smem + (size_t)s * kStageBytes;
+        mbar_expect_tx(&full_bar[s], (uint32_t)kStageBytes);
+        const int kcoord = k_base + k * kStageK;
+        tma_load_2d(st, &tmap_a0, kcoord, a_row, &full_bar[s]);
+        if (DUAL) tma_load_2d(st + kATileBytes, &tmap_a1, kcoord, a_row, &full_bar[s]);
+        tma_load_2d(st + NACC * kATileBytes, &tmap_b, kcoord, m0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int k = 0; k < ksteps && !abort_s; ++k) {
+        const int s = k % STAGES;
+        const uint32_t phase = (uint32_t)(k / STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], phase)) {
+          abort_s = 1;
+          atomicExch(&g_dense_error, 2);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(smem + (size_t)s * kStageBytes);
+        const uint64_t da0 = umma_desc(a0), da1 = umma_desc(a0 + kATileBytes),
+                       db = umma_desc(a0 + NACC * kATileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kStageK / 16; ++kk) {
+          const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, da0 + 2 * kk, db + 2 * kk, kIdesc, acc);
+          if (DUAL) umma_bf16(tmem_base + NTOK, da1 + 2 * kk, db + 2 * kk, kIdesc, acc);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (!abort_s) umma_commit(&acc_bar);
+    }
+  } else {
+    ok = mbar_wait(&acc_bar, 0u);  // every MMA of this CTA has read its operands
+    if (!ok) {
+      abort_s = 1;
+      atomicExch(&g_dense_error, 3);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+  cluster.sync();  // every CTA of the cluster is past its last MMA: the rings are free
+
+  if (warp >= 2 && ok) {
+    // ---- TMEM -> registers -> the owner's ring memory ----
+    const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;  // rows [32 grp, 32 grp + 32) of the block
+    const int nl = q * 32 + lane;     // feature inside the tile
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(grp * 32);
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) {
+      float v[32];
+      tmem_ld32(lane_addr + (uint32_t)(a * NTOK), v);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const int t = grp * 32 + c, owner = t / TOK, tl = t % TOK;
+        cluster.map_shared_rank(part, owner)[(size_t)(crank * TOK + tl) * kStride + a * 128 + nl] =
+            v[c];
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  cluster.sync();  // all partials delivered
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+  if (warp < 2 || abort_s) return;
+
+  // ---- final pass: this CTA owns rows [crank * TOK, (crank + 1) * TOK) of the block ----
+  const int et = threadIdx.x - 64;  // 0..511
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) {
+    const int e = et + i * 512;
+    const int tl = e / 128, nl = e % 128;
+    const int tok = m0 + crank * TOK + tl;
+    if (tok >= n_rows) continue;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int r = 0; r < CL; ++r) {
+      s0 += part[(size_t)(r * TOK + tl) * kStride + nl];
+      if (DUAL) s1 += part[(size_t)(r * TOK + tl) * kStride + 128 + nl];
+    }
+    const int f = a_row + nl;
+    if (DUAL) {
+      const float g = s0 + (bias != nullptr ? bias[f] : 0.f);
+      float h = 0.f;
+      if (g > 0.f)
+        h = __bfloat162float(__float2bfloat16_rn(g)) * __bfloat162float(__float2bfloat16_rn(s1));
+      out[(size_t)tok * ld_out + f] = __float2bfloat16_rn(h);
+    } else {
+      const int rid = row_ids != nullptr ? row_ids[tok] : tok;
+      out[(size_t)rid * ld_out + f] = __float2bfloat16_rn(s0);
+    }
+  }
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -707,6 +888,72 @@ int launch_persistent(const CUtensorMap& map_a0, const CUtensorMap& map_a1, cons
   return check_launch("b200_twell_gated_t2d_hybrid (dense rows, persistent)");
 }
 
+template <int CL, bool DUAL>
+int launch_dense_splitk_cl(const void* a0, const void* a1, int64_t a_rows, const void* b,
+                           int64_t b_rows, int64_t K, const float* bias, void* out,
+                           const int* row_ids, int64_t ld_out, int64_t cap, cudaStream_t stream) {
+  constexpr int STAGES = DUAL ? 4 : 5;
+  CUtensorMap map_a0, map_a1, map_b;
+  if (int rc = make_map(&map_a0, a0, a_rows, K, 128)) return rc;
+  if (int rc = make_map(&map_a1, a1, a_rows, K, 128)) return rc;
+  if (int rc = make_map(&map_b, b, b_rows, K, 128)) return rc;
+  const size_t smem = (size_t)STAGES * ((DUAL ? 2 : 1) * kATileBytes + 128 * 128) + 1024;
+  auto kern = dense_rows_gemm_splitk_kernel<CL, STAGES, DUAL>;
+  static size_t granted[64] = {0};
+  if (int rc = ensure_dynamic_smem(kern, smem, granted, "b200_twell_gated_t2d_hybrid")) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(a_rows / 128 * CL), (unsigned)((cap + 127) / 128), 1);
+  cfg.blockDim = dim3(kThreadsDenseWide, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (CL == 8) {  // clusters of 8 of a 160-190 KB CTA: only a limited number is resident at once
+    static int fit[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (fit[dev] == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = -1;
+      }
+      fit[dev] = n;
+    }
+    if ((int64_t)cfg.gridDim.x / CL * cfg.gridDim.y > fit[dev])
+      return fail(B200_EUNSUPPORTED, "dense rows (split-k): clusters of 8 do not fit one wave");
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_a0, map_a1, map_b, bias,
+                                     static_cast<__nv_bfloat16*>(out), row_ids, (int)cap, (int)K,
+                                     (int)ld_out);
+  if (e != cudaSuccess)
+    return fail(B200_ECUDA, "b200_twell_gated_t2d_hybrid (dense rows, split-k): launch: %s",
+                cudaGetErrorString(e));
+  return B200_OK;
+}
+
+template <bool DUAL>
+int launch_dense_splitk(int cl, const void* a0, const void* a1, int64_t a_rows, const void* b,
+                        int64_t b_rows, int64_t K, const float* bias, void* out,
+                        const int* row_ids, int64_t ld_out, int64_t cap, cudaStream_t stream) {
+  if (cl == 8) {
+    const int rc = launch_dense_splitk_cl<8, DUAL>(a0, a1, a_rows, b, b_rows, K, bias, out,
+                                                   row_ids, ld_out, cap, stream);
+    if (rc != B200_EUNSUPPORTED) return rc;
+    cl = 4;
+  }
+  if (cl == 4)
+    return launch_dense_splitk_cl<4, DUAL>(a0, a1, a_rows, b, b_rows, K, bias, out, row_ids,
+                                           ld_out, cap, stream);
+  return launch_dense_splitk_cl<2, DUAL>(a0, a1, a_rows, b, b_rows, K, bias, out, row_ids, ld_out,
+                                         cap, stream);
+}
+
 template <bool DUAL>
 int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void* b,
                       int64_t b_rows, int64_t K, const float* bias, void* out, const int* row_ids,
@@ -747,6 +994,26 @@ int launch_dense_gemm(const void* a0, const void* a1, int64_t a_rows, const void
     if (int rc = make_map(&map_a0, a0, a_rows, K, 128, KS)) return rc;
     if (int rc = make_map(&map_a1, a1, a_rows, K, 128, KS)) return rc;
     if (int rc = make_map(&map_b, b, b_rows, K, kDenseTok, KS)) return rc;
+  }
+  // Host-known row count of at most 512: split-k over a cluster, 128 features x 128 rows per
+  // tile (B200_DENSE_SPLITK=0 switches it off).  The largest cluster whose grid is one wave;
+  // two CTAs per tile are also taken when that needs two waves.
+  static const bool splitk_on = [] {
+    const char* e = getenv("B200_DENSE_SPLITK");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  if (KS == 64 && splitk_on && n_rows_ptr == nullptr && cap <= 512) {
+    const int64_t tiles128 = a_rows / 128, blocks = (cap + 127) / 128;
+    const int sms = sm_count();
+    int cl = 0;
+    for (int c : {8, 4, 2})
+      if (cl == 0 && tiles128 * c * blocks <= sms && K % (c * 64) == 0 && K / c >= 256) cl = c;
+    if (cl == 0 && tiles128 * 2 * blocks <= 2 * sms && K % 128 == 0 && K >= 512) cl = 2;
+    if (cl != 0) {
+      const int rc = launch_dense_splitk<DUAL>(cl, a0, a1, a_rows, b, b_rows, K, bias, out, row_ids,
+                                               ld_out, cap, stream);
+      if (rc != B200_EUNSUPPORTED) return rc;
+    }
   }
   // Host-known row count and enough 256-token tiles to fill the GPU: one CTA per SM on
   // 256-token tiles with sixteen epilogue warps (B200_DENSE_WIDE=0 keeps the 128-token tiles).

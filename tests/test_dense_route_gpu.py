@@ -129,7 +129,7 @@ def test_small_calls_keep_the_gather_kernel():
     hybrid.destroy()
 
 
-@pytest.mark.parametrize("m", [200, 1024])
+@pytest.mark.parametrize("m", [40, 128, 200, 512, 1024])   # up to 512 rows: the split-k GEMMs
 def test_all_rows_dense_with_gate_bias(m):
     """dense_all_tokens: no slab at all; also covers the explicit (not folded) gate bias and a
     token count that is not a multiple of the 128-token tile."""
@@ -139,7 +139,7 @@ def test_all_rows_dense_with_gate_bias(m):
     ref = fo.dense_ffn(x, ffn.gate, ffn.up, ffn.down, gate_bias=ffn.gate_bias)
     mod = twell.TwELLGatedMLP(7030, ffn.gate.to(DEV), ffn.up.to(DEV), ffn.down.to(DEV))
     mod.set_gate_bias(ffn.gate_bias)
-    mod.enable_dense_route(dense_all_tokens=128)
+    mod.enable_dense_route(dense_all_tokens=32)
     y = mod(x.to(DEV))
     torch.cuda.synchronize()
     assert _lib.load_library().b200_twell_hybrid_status() == 0
