@@ -17,7 +17,8 @@
 //   2  the CTAs of a tile exchange their counts (one DSMEM word each, one cluster barrier),
 //      slab words are written in ascending neuron order, the true count by rank 0;
 //   3  (fused) for the CTA's stored entries, eight at a time: every warp requests its
-//      d_model/8 column slice of the eight down rows, warp q also the whole up row of entry q;
+//      d_model/8 column slice of the eight down rows, warp q also the whole up row of entry q
+//      (the first batch already before the count exchange of phase 2 has completed);
 //      u = x . up, h = z * u with the contraction kernel's roundings, then
 //      acc[columns] += h * down: one memory round trip per eight entries;
 //   4  (fused) each rank sums d_model / CL columns of the cluster's CTAs through DSMEM, the
@@ -174,6 +175,7 @@ twell_gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   uint32_t mask[NBAL];
   float zv[NBAL];
   int mine = 0;
+  const int cap = slab_w - 1;
   if (warp == 0) {
 #pragma unroll
     for (int b = 0; b < NBAL; ++b) {
@@ -182,8 +184,49 @@ twell_gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       mine += __popc(mask[b]);
     }
     if (lane < CL) cluster.map_shared_rank(cnt_s, lane)[crank] = mine;
+    if (FUSED) {
+      // Tentative entry list: this CTA's first `cap` positives.  The entries the slab keeps
+      // are a prefix of it (entry k is stored iff prefix + k < cap), so their rows can be
+      // requested before the counts have crossed the cluster.
+      int before = 0;
+#pragma unroll
+      for (int b = 0; b < NBAL; ++b) {
+        const int k = before + __popc(mask[b] & lanemask_lt());
+        if (((mask[b] >> lane) & 1u) && k < cap)
+          ent_s[k] = (uint32_t)(nb + b * 32 + lane) | (bf16_bits(zv[b]) << 16);
+        before += __popc(mask[b]);
+      }
+      if (lane == 0) n_ent_s = min(mine, cap);
+    }
   }
-  cluster.sync();
+
+  // ---- phase 3, first half: row requests of a batch of eight entries ---------------------
+  const uint4* up_lane = reinterpret_cast<const uint4*>(up) + lane;
+  const uint4* down_slice = reinterpret_cast<const uint4*>(down) + warp * (D / 64) + lane;
+  // Every warp: its column slice of the batch's down rows; warp q: the whole up row of entry q.
+  auto request_rows = [&](int e0, int limit, uint4 (&dv)[8][NS], uint4 (&uv)[GATED ? DI : 1]) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const bool live = e0 + q < limit;
+      const size_t roff = live ? (size_t)(ent_s[e0 + q] & 0xFFFFu) * (D / 8) : 0;
+#pragma unroll
+      for (int j = 0; j < NS; ++j)
+        dv[q][j] = live ? ldg_stream(down_slice + roff + j * 32) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (GATED && e0 + warp < limit) {  // the same decision in all lanes
+      const size_t roff = (size_t)(ent_s[e0 + warp] & 0xFFFFu) * (D / 8);
+#pragma unroll
+      for (int it = 0; it < (GATED ? DI : 1); ++it) uv[it] = ldg_stream(up_lane + roff + it * 32);
+    }
+  };
+  uint4 dv0[8][NS];
+  uint4 uv0[GATED ? DI : 1];
+  if (FUSED) {
+    __syncthreads();  // tentative list visible
+    request_rows(0, n_ent_s, dv0, uv0);
+  }
+
+  cluster.sync();  // counts delivered
   if (warp == 0) {
     int prefix = 0, total = 0;
 #pragma unroll
@@ -194,50 +237,31 @@ twell_gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     }
     uint32_t* slab = packed + (size_t)tile * slab_w;
     if (crank == 0 && lane == 0) slab[0] = (uint32_t)total;
-    const int cap = slab_w - 1;
     int before = 0;  // positives of this CTA in lower ballots
 #pragma unroll
     for (int b = 0; b < NBAL; ++b) {
       const int k = before + __popc(mask[b] & lanemask_lt());
-      if (((mask[b] >> lane) & 1u) && prefix + k < cap) {
-        const uint32_t word = (uint32_t)(nb + b * 32 + lane) | (bf16_bits(zv[b]) << 16);
-        slab[1 + prefix + k] = word;
-        ent_s[k] = word;
-      }
+      if (((mask[b] >> lane) & 1u) && prefix + k < cap)
+        slab[1 + prefix + k] = (uint32_t)(nb + b * 32 + lane) | (bf16_bits(zv[b]) << 16);
       before += __popc(mask[b]);
     }
-    if (lane == 0) n_ent_s = max(0, min(mine, cap - prefix));
+    if (lane == 0) n_ent_s = max(0, min(mine, cap - prefix));  // entries the slab keeps
   }
   if (!FUSED) return;
   __syncthreads();
 
-  // ---- phase 3 ---------------------------------------------------------------------
+  // ---- phase 3, second half ------------------------------------------------------------
   const int n = n_ent_s;
   float acc[NS * 8];
 #pragma unroll
   for (int c = 0; c < NS * 8; ++c) acc[c] = 0.f;
-  const uint4* up_lane = reinterpret_cast<const uint4*>(up) + lane;
-  const uint4* down_slice = reinterpret_cast<const uint4*>(down) + warp * (D / 64) + lane;
-  for (int e0 = 0; e0 < n; e0 += 8) {
-    uint4 dv[8][NS];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const bool live = e0 + q < n;
-      const size_t roff = live ? (size_t)(ent_s[e0 + q] & 0xFFFFu) * (D / 8) : 0;
-#pragma unroll
-      for (int j = 0; j < NS; ++j)
-        dv[q][j] = live ? ldg_stream(down_slice + roff + j * 32) : make_uint4(0u, 0u, 0u, 0u);
-    }
+  auto consume_rows = [&](int e0, uint4 (&dv)[8][NS], uint4 (&uv)[GATED ? DI : 1]) {
     float h = 0.f;
     if (e0 + warp < n) {  // the same decision in all lanes
       const uint32_t word = ent_s[e0 + warp];
       const __nv_bfloat16 gval = __ushort_as_bfloat16((unsigned short)(word >> 16));
       if (GATED) {
-        uint4 uv[DI];
-        const size_t roff = (size_t)(word & 0xFFFFu) * (D / 8);
-#pragma unroll
-        for (int it = 0; it < DI; ++it) uv[it] = ldg_stream(up_lane + roff + it * 32);
-        const float u = dot_up<DI, HP>(uv, xv);
+        const float u = dot_up<DI, HP>(reinterpret_cast<uint4 (&)[DI]>(uv), xv);
         h = HP ? __bfloat162float(gval) * u
                : __bfloat162float(__hmul(gval, __float2bfloat16_rn(u)));
       } else {
@@ -248,7 +272,7 @@ twell_gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     __syncthreads();
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      const float hq = hs[q];  // 0 for a padding entry
+      const float hq = hs[q];  // 0 for a padding entry or one the slab dropped
 #pragma unroll
       for (int j = 0; j < NS; ++j) {
         const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&dv[q][j]);
@@ -271,6 +295,13 @@ twell_gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       }
     }
     __syncthreads();  // hs is rewritten by the next batch
+  };
+  if (n > 0) consume_rows(0, dv0, uv0);
+  for (int e0 = 8; e0 < n; e0 += 8) {
+    uint4 dv[8][NS];
+    uint4 uv[GATED ? DI : 1];
+    request_rows(e0, n, dv, uv);
+    consume_rows(e0, dv, uv);
   }
 
   // ---- phase 4 ---------------------------------------------------------------------
