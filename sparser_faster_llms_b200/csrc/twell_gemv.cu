@@ -354,7 +354,7 @@ twell_gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     __threadfence();
 #pragma unroll
     for (int i = 0; i < PPT; ++i) sum[i] = make_float2(0.f, 0.f);
-#pragma unroll 8
+#pragma unroll 32
     for (int t = 0; t < tiles; ++t) {
 #pragma unroll
       for (int i = 0; i < PPT; ++i) {
