@@ -425,7 +425,8 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
     const int c = 2 * (tid + k * NTHREADS);
     if (c >= cols) break;
     float s0 = 0.f, s1 = 0.f;
-    for (int q = 0; q < nc; ++q) {
+#pragma unroll 4
+    for (int q = 0; q < nc; ++q) {  // independent loads: four in flight
       const float2 v = __ldcg(reinterpret_cast<const float2*>(tok_part + (size_t)q * D + c));
       s0 += v.x;
       s1 += v.y;
