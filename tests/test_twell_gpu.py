@@ -461,3 +461,46 @@ def test_kernel_sweep_shape_against_the_oracle(m):
     want = fo.gated_t2d(x[:mo], slab[:mo], ffn.up, ffn.down)
     _, rel = fo.max_abs_and_rel_l2(got[:mo].float().cpu(), want)
     assert rel < REL_L2_SAME_SLAB, rel
+
+
+@pytest.mark.parametrize("group", [3, 4])
+def test_grouped_launch_order_of_the_large_m_kernels_is_bit_exact(group):
+    """The grouped CTA order (token blocks walked in groups before the next neuron tile) only
+    switches itself on for weight matrices beyond L2 size; a child process forces it
+    (B200_TC_RASTER, read once per process) on a small exact-arithmetic case with a ragged last
+    group (6 token blocks of 256 in groups of 3 and 4) and checks pack and the all-dense route."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    code = textwrap.dedent("""
+        import numpy as np, torch
+        from oracle import ffn_oracle as fo, twell_format as tf
+        from sparser_faster_llms_b200 import _lib, synthetic, twell
+        dev = torch.device("cuda:0")
+        m, d, h = 1300, 512, 1024
+        x, gate, up, down = synthetic.dyadic_case(m, d, h, seed=77)
+        want = tf.pack_preactivations(fo.gate_preactivation(x, gate).numpy(), 8)
+        xg, gg = x.to(dev), gate.to(dev)
+        for kernel in (7, 4):
+            p = twell.allocate_packed_output(m, h, device=dev)
+            _lib.call("b200_twell_pack_select", dev, xg.data_ptr(), gg.data_ptr(), None,
+                      p.data_ptr(), m, d, h, 8, kernel)
+            torch.cuda.synchronize()
+            got = p.cpu().view(torch.int32).numpy().view(np.uint32)
+            assert np.array_equal(got, want), kernel
+        ug, dt = up.to(dev), down.to(dev).t().contiguous()
+        hws = torch.empty(m, h, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(m, d, device=dev, dtype=torch.bfloat16)
+        _lib.call("b200_dense_gated_mlp", dev, xg.data_ptr(), gg.data_ptr(), None, ug.data_ptr(),
+                  dt.data_ptr(), hws.data_ptr(), out.data_ptr(), m, d, h)
+        torch.cuda.synchronize()
+        ref = fo.dense_ffn(x, gate, up, down)
+        assert fo.max_abs_and_rel_l2(out.float().cpu(), ref)[1] < 1.2e-2
+        print("grouped order ok")
+    """)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True,
+                         env={**os.environ, "B200_TC_RASTER": str(group),
+                              "PYTHONPATH": root + os.pathsep + os.environ.get("PYTHONPATH", "")})
+    assert res.returncode == 0 and "grouped order ok" in res.stdout, res.stderr[-2000:]
