@@ -169,3 +169,19 @@ def test_hybrid_entry_point_rejects_bad_arguments():
     rc = lib.b200_twell_gated_t2d_hybrid(p, p, p, None, p, p, p, p, m, d, h, 8, 0, 100, 0,
                                          p, need, None, 0, None)
     assert rc == -1
+
+
+def test_all_rows_dense_on_256_token_tiles_for_both_products():
+    """4096 tokens at D 2048 / d_ff 1024: both GEMMs of the all-dense route have 128 tiles of
+    256 tokens, i.e. both run the one-CTA-per-SM form with sixteen epilogue warps."""
+    m, d, h = 4096, 2048, 1024
+    ffn = synthetic.make_ffn(d, h, seed=900, density=0.05)
+    x = synthetic.make_tokens(m, d, seed=901)
+    ref = fo.dense_ffn(x, ffn.gate, ffn.up, ffn.down)
+    mod = twell.TwELLGatedMLP(7040, ffn.gate.to(DEV), ffn.up.to(DEV), ffn.down.to(DEV))
+    mod.enable_dense_route(dense_all_tokens=1024)
+    y = mod(x.to(DEV))
+    torch.cuda.synchronize()
+    assert _lib.load_library().b200_twell_hybrid_status() == 0
+    assert row_rel_l2(y, ref).max() < REL_L2_ROW
+    mod.destroy()
