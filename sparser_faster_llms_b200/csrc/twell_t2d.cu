@@ -84,45 +84,29 @@ __device__ __forceinline__ void far_push(const FusedAr& ar, size_t inbox_off, si
 }
 
 // Sum over ranks, in rank order, of the bf16 pairs of one position; `mine` is this rank's.
-// The first poll of every peer's slot is issued before any of them is examined, so that the
-// round trips to the inbox overlap instead of adding up (seven peers at world 8).
 __device__ __forceinline__ float2 far_gather(const FusedAr& ar, const unsigned char* my_inbox,
                                              size_t pair, uint32_t mine, uint32_t e,
                                              uint32_t* err, uint32_t& limit) {
-  uint32_t payload[8], flag[8];
-#pragma unroll
-  for (int p = 0; p < 8; ++p) {
-    payload[p] = mine;
-    flag[p] = e;
-    if (p < ar.world && p != ar.rank) {
-      const uint2* src =
-          reinterpret_cast<const uint2*>(my_inbox + (size_t)p * (size_t)ar.slot_bytes) + pair;
-      asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
-                   : "=r"(payload[p]), "=r"(flag[p])
-                   : "l"(src)
-                   : "memory");
-    }
-  }
   float s0 = 0.f, s1 = 0.f;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
     if (p >= ar.world) continue;
-    if (p != ar.rank && flag[p] != e) {
-      const uint2* src =
-          reinterpret_cast<const uint2*>(my_inbox + (size_t)p * (size_t)ar.slot_bytes) + pair;
-      uint32_t spins = 0;
+    uint32_t payload = mine;
+    if (p != ar.rank) {
+      const uint2* src = reinterpret_cast<const uint2*>(my_inbox + (size_t)p * (size_t)ar.slot_bytes) + pair;
+      uint32_t flag = 0, spins = 0;
       do {
         asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
-                     : "=r"(payload[p]), "=r"(flag[p])
+                     : "=r"(payload), "=r"(flag)
                      : "l"(src)
                      : "memory");
-      } while (flag[p] != e && ++spins < limit);
-      if (flag[p] != e) {
+      } while (flag != e && ++spins < limit);
+      if (flag != e) {
         atomicExch(err, 0x100u + (uint32_t)p);  // this peer never arrived
         limit = kFarShortSpinLimit;             // the remaining waits of this thread drain fast
       }
     }
-    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&payload[p]));
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&payload));
     s0 += f.x;
     s1 += f.y;
   }
@@ -441,8 +425,7 @@ twell_t2d_kernel(const __nv_bfloat16* x, const uint32_t* __restrict__ packed,
     const int c = 2 * (tid + k * NTHREADS);
     if (c >= cols) break;
     float s0 = 0.f, s1 = 0.f;
-#pragma unroll 4
-    for (int q = 0; q < nc; ++q) {  // independent loads: four in flight
+    for (int q = 0; q < nc; ++q) {
       const float2 v = __ldcg(reinterpret_cast<const float2*>(tok_part + (size_t)q * D + c));
       s0 += v.x;
       s1 += v.y;
