@@ -252,6 +252,30 @@ def make_peer_allreduce(args, device, dist_on):
     return None, f"nccl all-reduce (peer all-reduce unavailable: {why or 'on another rank'})"
 
 
+def one_token_layer(B: int, d: int, hl: int, par) -> bool:
+    """Whether b200_twell_gated_mlp serves the call with the one-token kernel (one launch):
+    a single token, d_model 2048 / 4096, a tile count that fits clusters of four (33 on
+    B200), the 1 MiB workspace large enough for the partial rows, no d_ff sharding."""
+    tiles = hl // 256
+    return (par is None and B == 1 and d in (2048, 4096) and tiles <= 33
+            and 4096 * 4 + tiles * d * 4 <= (1 << 20)
+            and os.environ.get("B200_ONE_TOKEN", "2") == "2")
+
+
+def pack_kernel_name(B: int, d: int, hl: int) -> str:
+    """The kernel b200_twell_pack launches for this call (csrc/c_api.cu)."""
+    tiles = hl // 256
+    if B == 1 and d in (2048, 4096):
+        return "twell_gemv_kernel"
+    if B <= 16:
+        return "twell_pack_kernel"
+    if B <= 32:
+        return "twell_pack_tc_splitk_wide_kernel"
+    if B <= 256 and tiles * 2 * -(-B // 128) <= 148:
+        return "twell_pack_tc_splitk_mid_kernel"
+    return "twell_pack_tc_wide_kernel" if B > 64 else "twell_pack_tc_kernel"
+
+
 def run_ours(args):
     import torch.distributed as dist
     from sparser_faster_llms_b200 import _lib, twell
@@ -382,9 +406,7 @@ def run_ours(args):
                    "dense_cublas_bf16_ms_per_step": ms_dense,
                    "ffn_algorithmic_gbs": ffn_bytes / (ms_step / L * 1e-3) / 1e9},
         "roofline": {"bound": "hbm",
-                     "kernel": ("twell_pack_kernel" if B <= 16 else
-                                "twell_pack_tc_splitk_kernel" if B <= 32 else
-                                "twell_pack_tc_kernel"),
+                     "kernel": pack_kernel_name(B, d, hl),
                      "achieved": achieved,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": achieved / peak,
@@ -392,7 +414,9 @@ def run_ours(args):
                      # 33.73 MB for 33.71 MB of algorithmic bytes; scaled to this launch
                      "traffic": float(pack_bytes) * NCU_DRAM_OVER_ALGORITHMIC,
                      "us_per_launch": ms_pack * 1e3, "algorithmic_bytes": pack_bytes},
-        "gpu_launches": args.steps * L * (3 if (par is not None and far is None) else 2),
+        # one token on one GPU: pack and contraction are ONE launch (the GEMV kernel)
+        "gpu_launches": args.steps * L * (3 if (par is not None and far is None) else
+                                          1 if one_token_layer(B, d, hl, par) else 2),
         "clocks": clocks,
         "energy": energy_row,
     }
