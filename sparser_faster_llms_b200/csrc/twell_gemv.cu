@@ -354,7 +354,8 @@ twell_gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     __threadfence();
 #pragma unroll
     for (int i = 0; i < PPT; ++i) sum[i] = make_float2(0.f, 0.f);
-#pragma unroll 32
+    constexpr int kRowsInFlight = 32 / PPT;  // partial rows whose loads are in flight together
+#pragma unroll kRowsInFlight
     for (int t = 0; t < tiles; ++t) {
 #pragma unroll
       for (int i = 0; i < PPT; ++i) {
