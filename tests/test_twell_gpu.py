@@ -504,3 +504,31 @@ def test_grouped_launch_order_of_the_large_m_kernels_is_bit_exact(group):
                          env={**os.environ, "B200_TC_RASTER": str(group),
                               "PYTHONPATH": root + os.pathsep + os.environ.get("PYTHONPATH", "")})
     assert res.returncode == 0 and "grouped order ok" in res.stdout, res.stderr[-2000:]
+
+
+@pytest.mark.parametrize("m", [1, 2, 15, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256,
+                               257, 300])
+@pytest.mark.parametrize("d,h", [(2048, 2048), (512, 768), (4096, 1024)])
+def test_automatic_kernel_choice_at_every_token_count_boundary(m, d, h):
+    """b200_twell_gated_mlp with the library's own kernel choice on both sides of every token
+    count at which the choice changes (GEMV / mma.sync / tcgen05 split-k with 32- and 128-token
+    tiles / 256-token tiles): slab bit-exact on exact-arithmetic inputs, output against the
+    oracle fed that slab."""
+    from sparser_faster_llms_b200 import _lib
+    x, gate, up, down = synthetic.dyadic_case(m, d, h, seed=3 * m + d + h)
+    want = tf.pack_preactivations(fo.gate_preactivation(x, gate).numpy(), 8)
+    xg, gg, ug, dg = x.to(DEV), gate.to(DEV), up.to(DEV), down.to(DEV)
+    packed = twell.allocate_packed_output(m, h, device=DEV)
+    packed.zero_()
+    out = torch.empty_like(xg)
+    ws_ptr, ws_bytes = _lib.workspace(DEV)
+    _lib.call("b200_twell_gated_mlp", DEV, xg.data_ptr(), gg.data_ptr(), None, ug.data_ptr(),
+              dg.data_ptr(), packed.data_ptr(), out.data_ptr(), m, d, h, 8, 0, ws_ptr, ws_bytes)
+    torch.cuda.synchronize()
+    slab = to_np_u32(packed)
+    assert np.array_equal(slab, want)
+    rows = min(m, 6)
+    ref = fo.gated_t2d(x[:rows], slab[:rows], up, down)
+    got = out[:rows].float().cpu()
+    assert fo.max_abs_and_rel_l2(got, ref)[1] < 2e-3
+    assert _lib.load_library().b200_twell_pack_tc_status() == 0
