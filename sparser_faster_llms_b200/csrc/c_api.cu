@@ -183,9 +183,9 @@ int b200_twell_pack_select(const void* x, const void* w, const float* bias, void
   if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 3u))
     return fail(B200_EALIGN, "%s: bias is not 4-byte aligned", fn);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // Up to one 32-token tile the weight stream is read once and the split-k mma.sync
-  // kernel is HBM-bound; beyond that the tcgen05 kernel reuses each weight tile for up
-  // to 128 tokens.
+  // Up to one 32-token tile the weight stream is read once and the split-k kernels are
+  // HBM-bound; 33..256 tokens take 128-token tiles, still split over a cluster while that grid
+  // is one wave; beyond that the tcgen05 tile kernel reuses each weight tile for 256 tokens.
   // Measured on B200 (D 2048, H 8192): up to 16 tokens the mma.sync cluster kernel is
   // fastest (9.6-9.9 us vs 11.7-12.4); at 17..32 tokens its mma work per CTA grows and the
   // tcgen05 split-k kernel wins (12.5 vs 13.9 us).

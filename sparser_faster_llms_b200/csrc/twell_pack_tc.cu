@@ -1,4 +1,10 @@
-// Gate projection + ReLU + TwELL pack on the 5th-generation tensor cores (large M).
+// Gate projection + ReLU + TwELL pack on the 5th-generation tensor cores.
+//
+// Kernels of this file, by token count: twell_pack_tc_splitk_(wide_)kernel (17..32 tokens, D
+// split over a cluster), twell_pack_tc_splitk_mid_kernel (33..256, 128-token tiles, D split),
+// twell_pack_tc_wide_kernel (256-token tiles, one CTA per SM, sixteen epilogue warps: the
+// default above that) and twell_pack_tc_kernel, described first (64- / 128-token tiles, four
+// epilogue warps).
 //
 // CTA tile: one 256-neuron TwELL tile x NTOK tokens (64 or 128) x all of D.
 // Neurons ride the MMA M axis as two 128-row accumulators, tokens the N axis:
